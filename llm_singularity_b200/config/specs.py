@@ -32,6 +32,17 @@ class RMSNormSpec(PartSpec):
     kind: str = field(init=False, default="rmsnorm")
 
 
+@dataclass(frozen=True)
+class GroupRMSNormSpec(PartSpec):
+    """RMS norm in ``groups`` equal consecutive parts of the vector, each with its own mean of
+    squares, and one weight over the whole vector; one group is the plain RMS norm."""
+
+    size: int = 0
+    eps: float = 1e-5
+    groups: int = 1
+    kind: str = field(init=False, default="group_rmsnorm")
+
+
 # ---------------------------------------------------------------- position encodings
 @dataclass(frozen=True)
 class Llama3RopeScaling:
@@ -45,12 +56,14 @@ class Llama3RopeScaling:
 
 @dataclass(frozen=True)
 class RotarySpec(PartSpec):
-    """Rotary position encoding with split-half pairing (i, i + rotary_dim/2)."""
+    """Rotary position encoding.  ``pairing`` "half" rotates dims (i, i + rotary_dim/2) together,
+    "adjacent" rotates dims (2i, 2i + 1); pair i turns by ``pos * theta^(-2i / rotary_dim)``."""
 
     head_dim: int = 0
     rotary_dim: int = 0           # leading dims of each head that rotate
     theta: float = 10000.0
     scaling: Optional[Llama3RopeScaling] = None
+    pairing: str = "half"
     kind: str = field(init=False, default="rotary")
 
 
@@ -78,6 +91,54 @@ class AttentionSpec(PartSpec):
     kind: str = field(init=False, default="attention")
 
 
+@dataclass(frozen=True)
+class LinearRecurrenceSpec(PartSpec):
+    """Linear attention with a matrix state per head: ``S <- diag(a) S + b v^T``, ``o = S^T q``.
+
+    ``gate`` says where a and b come from.  "fixed_decay": a is one constant per head (``decay``)
+    and b is a key projection; "forget": a is a forget gate per channel with a learnt floor,
+    ``a = floor + (1 - floor) * sigmoid(W_f x + bias)``, and ``b = 1 - a`` (no key).  The
+    activations of the query, key and value projections, how the output is normed (over all heads
+    together, "all", or each head by itself with one weight of head size, "per_head") and whether a
+    sigmoid gate projection multiplies it are fields, so that relatives of the two shipped kinds
+    (``lightning`` and ``hgrn2``) are other settings of the same part."""
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    key_dim: int = 0              # per head: channels of q (and of k or the forget gate)
+    value_dim: int = 0            # per head
+    gate: str = "fixed_decay"
+    decay: Tuple[float, ...] = ()
+    q_activation: str = "silu"
+    k_activation: str = "silu"
+    v_activation: str = "none"
+    out_norm: str = "all"
+    out_gate: bool = False
+    eps: float = 1e-5
+    kind: str = field(init=False, default="linear_recurrence")
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(PartSpec):
+    """Causal softmax attention whose keys and values are made per head from one cached latent
+    vector per token, plus one rotated key part that all heads share.  Queries come through a
+    normed latent of their own.  ``reads_only``: the layer has no latent projection and reads
+    the cache another layer of the same shape writes."""
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    plain_dim: int = 0            # per head: query/key dims without rotation
+    rot_dim: int = 0              # query/key dims that carry the position
+    value_dim: int = 0            # per head
+    q_rank: int = 0
+    kv_rank: int = 0
+    scale: float = 0.0
+    eps: float = 1e-5
+    reads_only: bool = False
+    position: PartSpec = field(default_factory=NoPositionSpec)
+    kind: str = field(init=False, default="latent_attention")
+
+
 # -------------------------------------------------------------------- feed-forwards
 @dataclass(frozen=True)
 class GatedMLPSpec(PartSpec):
@@ -87,6 +148,41 @@ class GatedMLPSpec(PartSpec):
     intermediate_size: int = 0
     activation: str = "silu"
     kind: str = field(init=False, default="gated_mlp")
+
+
+@dataclass(frozen=True)
+class MoESpec(PartSpec):
+    """Routed gated experts, no bias: ``sum over the chosen e of down_e(act(gate_e u) * up_e u)``.
+
+    Router logits are 32-bit; ``score`` turns them into scores ("sigmoid", or "softmax" over all
+    experts); the ``top`` largest are chosen; ``renormalize`` divides the chosen scores by their
+    sum.  ``weight_on`` says what a score multiplies: the expert's "input" (``u = s x``) or its
+    "output"."""
+
+    hidden_size: int = 0
+    expert_size: int = 0
+    num_experts: int = 0
+    top: int = 1
+    activation: str = "silu"
+    score: str = "sigmoid"
+    renormalize: bool = False
+    weight_on: str = "input"
+    kind: str = field(init=False, default="moe")
+
+
+@dataclass(frozen=True)
+class TokenSideSpec(PartSpec):
+    """A second, narrow embedding of the token that enters a block after its feed-forward:
+    ``x += unit(proj(act(gate x) * e)) * w`` with ``e`` this block's ``dim`` columns (from
+    ``offset``) of a table held beside the embedding, and ``unit`` the division by the root
+    mean square."""
+
+    hidden_size: int = 0
+    dim: int = 0
+    offset: int = 0
+    activation: str = "gelu_tanh"
+    eps: float = 1e-5
+    kind: str = field(init=False, default="token_side")
 
 
 # --------------------------------------------------------------------------- blocks
@@ -99,6 +195,24 @@ class BlockSpec(PartSpec):
     mixer_norm: PartSpec = None
     ffn_norm: PartSpec = None
     kind: str = field(init=False, default="pre_norm")
+
+
+@dataclass(frozen=True)
+class PostNormBlockSpec(PartSpec):
+    """x <- norm1(alpha x + mixer(x)); x <- norm2(alpha x + ffn(x))   (the "post_norm" arrangement:
+    the sublayers read the stream itself, the norm follows the sum).  ``ffn`` None: no second
+    step.  ``gated_residual``: each sublayer's result is multiplied by ``sigmoid(W x + b)`` of the
+    sublayer's input before the sum.  ``side``: a per-token input added last."""
+
+    mixer: PartSpec = None
+    ffn: Optional[PartSpec] = None
+    mixer_norm: PartSpec = None
+    ffn_norm: Optional[PartSpec] = None
+    alpha: float = 1.0
+    gated_residual: bool = False
+    hidden_size: int = 0
+    side: Optional[TokenSideSpec] = None
+    kind: str = field(init=False, default="post_norm")
 
 
 @dataclass(frozen=True)
@@ -122,6 +236,7 @@ class LayerCall:
 class EmbeddingSpec(PartSpec):
     vocab_size: int = 0
     hidden_size: int = 0
+    side_size: int = 0            # columns of a second table of per-token inputs for the blocks (0: none)
     kind: str = field(init=False, default="embedding")
 
 

@@ -28,7 +28,7 @@ from .batch import StepEntry
 from .runner import ModelRunner
 
 ROUND_TO = 64            # each request's token count is rounded up to this when sizing the pool
-MAX_LIVE = 16
+MAX_LIVE = 4             # request slots (block-table rows and state rows): no more requests are live at a time
 
 
 def replay(runner: ModelRunner, lines: IO[str], out_dir: str, done: Optional[IO[str]] = None) -> int:
@@ -74,13 +74,14 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--max-requests", type=int, default=MAX_LIVE, help="request slots of the engine")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
     if ROUND_TO % args.page_size:
         ap.error(f"--page-size must divide {ROUND_TO}")
     capacity = -(-args.max_tokens // ROUND_TO) * ROUND_TO
     runner = ModelRunner(args.model, dtype=args.dtype, device=args.device, page_size=args.page_size,
-                         num_pages=capacity // args.page_size, max_requests=MAX_LIVE,
+                         num_pages=capacity // args.page_size, max_requests=args.max_requests,
                          max_model_len=capacity, verbose=True)
     replay(runner, sys.stdin, args.out)
     return 0

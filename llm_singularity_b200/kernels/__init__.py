@@ -773,6 +773,297 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
                   _p(out), _i(last - first), _i(ctx.max_q_len), *tail, skip, on)
 
 
+# ----------------------------------------------- rows of a stream that is normed after the sum
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x (32-bit) rounded to out's dtype."""
+    _req(x, "x", torch.float32)
+    _req(out, "out")
+    if out.shape != x.shape:
+        raise KernelError("cast_rows: shapes differ")
+    _call("rownorm", "lsb_cast_rows", _p(x), _p(out), _i(_dt(out)), _ll(x.numel()), _stream(out))
+
+
+def post_group_norm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                    groups: int, alpha: float, out: Optional[torch.Tensor], gate: Optional[torch.Tensor] = None,
+                    gate_bias: Optional[torch.Tensor] = None, keep_sum: bool = False, dtype=None) -> None:
+    """s = alpha * residual + delta * sigmoid(gate + gate_bias); y = the RMS norm of s in ``groups``
+    consecutive parts, times weight.  residual <- y (or s with ``keep_sum``), in place, 32-bit;
+    out <- y in the compute dtype (``out`` may be None).  ``gate`` may be a column slice of a wider
+    tensor (its row stride is passed on)."""
+    _req(residual, "residual", torch.float32, 2)
+    _req(weight, "weight", torch.float32, 1)
+    T, H = residual.shape
+    dt = out.dtype if out is not None else (delta.dtype if delta is not None else (dtype or torch.float32))
+    if out is not None:
+        _req(out, "out", dim=2)
+        if out.shape != (T, H):
+            raise KernelError("post_group_norm: out has another shape than residual")
+    if weight.shape[0] != H or groups <= 0 or H % groups:
+        raise KernelError(f"post_group_norm: weight {tuple(weight.shape)} / groups {groups} do not fit width {H}")
+    gate_stride = 0
+    if delta is not None:
+        _req(delta, "delta", dt, 2)
+        if delta.shape != (T, H):
+            raise KernelError("post_group_norm: delta has another shape than residual")
+    if gate is not None:
+        _req(gate, "gate", dt, 2, contiguous=False)
+        if delta is None or gate.shape != (T, H) or gate.stride(1) != 1:
+            raise KernelError("post_group_norm: the gate needs a delta and its shape, with unit column stride")
+        gate_stride = gate.stride(0)
+        if gate_bias is not None:
+            _req(gate_bias, "gate_bias", torch.float32, 1)
+    _call("rownorm", "lsb_post_group_norm", _p(residual), _p(delta), _p(gate), _ll(gate_stride), _p(gate_bias),
+          _p(weight), _p(out), _i(_F32 if dt == torch.float32 else _BF16), _i(T), _i(H), _i(groups), _f(alpha),
+          _f(eps), _i(1 if keep_sum else 0), _stream(residual))
+
+
+def gather_group_norm(residual: torch.Tensor, rows: torch.Tensor, weight: torch.Tensor, eps: float,
+                      groups: int, out: torch.Tensor) -> None:
+    """out[i] = group RMS norm of residual[rows[i]], times weight; residual unchanged."""
+    _req(residual, "residual", torch.float32, 2)
+    _req(rows, "rows", torch.int32, 1)
+    _req(weight, "weight", torch.float32, 1)
+    _req(out, "out", dim=2)
+    T, H = residual.shape
+    if out.shape != (rows.shape[0], H) or weight.shape[0] != H or groups <= 0 or H % groups:
+        raise KernelError("gather_group_norm: shapes disagree")
+    _call("rownorm", "lsb_gather_group_norm", _p(residual), _p(rows), _i(rows.shape[0]), _i(T), _p(weight),
+          _p(out), _i(_dt(out)), _i(H), _i(groups), _f(eps), _stream(out))
+
+
+def unit_add(residual: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
+             out: Optional[torch.Tensor]) -> None:
+    """residual += y / sqrt(mean(y^2) + eps) * weight (in place, 32-bit); out <- residual rounded."""
+    _req(residual, "residual", torch.float32, 2)
+    _req(y, "y", dim=2)
+    _req(weight, "weight", torch.float32, 1)
+    if y.shape != residual.shape or weight.shape[0] != residual.shape[1]:
+        raise KernelError("unit_add: shapes disagree")
+    if out is not None:
+        _req(out, "out", y.dtype, 2)
+        if out.shape != residual.shape:
+            raise KernelError("unit_add: out has another shape than residual")
+    _call("rownorm", "lsb_unit_add", _p(residual), _p(y), _p(weight), _p(out), _i(_dt(y)),
+          _i(residual.shape[0]), _i(residual.shape[1]), _f(eps), _stream(residual))
+
+
+def rows_norm_gate(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float,
+                   gate: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out = RMS norm of each of the ``groups`` parts of a 32-bit row, times ``weight`` (its index taken
+    modulo its length: one weight per part, or one over the row), times sigmoid(gate) if given."""
+    _req(x, "x", torch.float32, 2)
+    _req(weight, "weight", torch.float32, 1)
+    _req(out, "out", dim=2)
+    T, n = x.shape
+    if out.shape != (T, n) or groups <= 0 or n % groups or n % weight.shape[0]:
+        raise KernelError("rows_norm_gate: shapes disagree")
+    gate_stride = 0
+    if gate is not None:
+        _req(gate, "gate", out.dtype, 2, contiguous=False)
+        if gate.shape != (T, n) or gate.stride(1) != 1:
+            raise KernelError("rows_norm_gate: the gate must have x's shape and unit column stride")
+        gate_stride = gate.stride(0)
+    _call("rownorm", "lsb_rows_norm_gate", _p(x), _p(weight), _i(weight.shape[0]), _p(gate), _ll(gate_stride),
+          _p(out), _i(_dt(out)), _i(T), _i(n), _i(groups), _f(eps), _stream(out))
+
+
+def token_side_gate(g: torch.Tensor, table: torch.Tensor, token_ids: torch.Tensor, offset: int,
+                    activation: str, out: torch.Tensor) -> None:
+    """out[t, j] = act(g[t, j]) * table[token_ids[t], offset + j]."""
+    _req(g, "g", dim=2)
+    _req(table, "table", g.dtype, 2)
+    _req(token_ids, "token_ids", torch.int32, 1)
+    _req(out, "out", g.dtype, 2)
+    T, dim = g.shape
+    if out.shape != (T, dim) or token_ids.shape[0] != T or offset < 0 or offset + dim > table.shape[1]:
+        raise KernelError("token_side_gate: shapes disagree")
+    _call("rownorm", "lsb_token_side_gate", _p(g), _p(table), _p(token_ids), _p(out), _i(_dt(g)), _i(T), _i(dim),
+          _i(table.shape[1]), _i(offset), _i(table.shape[0]), _i(ACTIVATIONS.get(activation, 0) if activation != "none" else 0),
+          _stream(out))
+
+
+# ------------------------------------------------------------------ linear recurrence
+SCAN_GATES = {"fixed_decay": 0, "forget": 1}
+_SCAN_ACTS = {"none": 0, "silu": 1}
+
+
+def linear_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, key_dim: int,
+                value_dim: int, gate: str, decay: Optional[torch.Tensor], f_bias: Optional[torch.Tensor],
+                floor: Optional[torch.Tensor], q_act: str, k_act: str, v_act: str, state: torch.Tensor,
+                ctx, out: torch.Tensor) -> None:
+    """S <- diag(a) S + b v^T, o = S^T q per head and token, each request from its slot's state
+    (``state`` [slots, heads, value_dim, key_dim] 32-bit, updated in place); ``proj`` [T, columns] holds
+    the projections of q at ``q_off``, of k (or the forget gate) at ``k_off`` and of v at ``v_off``;
+    ``out`` [T, heads * value_dim] 32-bit."""
+    _req(proj, "proj", dim=2)
+    _req(state, "state", torch.float32, 4)
+    _req(out, "out", torch.float32, 2)
+    T, ld = proj.shape
+    if state.shape[1:] != (heads, value_dim, key_dim) or out.shape != (T, heads * value_dim) or ctx.n_tokens != T:
+        raise KernelError("linear_scan: state, out or the step do not fit the sizes")
+    if max(q_off, k_off) + heads * key_dim > ld or v_off + heads * value_dim > ld or min(q_off, k_off, v_off) < 0:
+        raise KernelError("linear_scan: a projection lies outside the rows of proj")
+    for name, t, n in (("decay", decay, heads), ("f_bias", f_bias, heads * key_dim), ("floor", floor, heads * key_dim)):
+        if t is not None:
+            _req(t, name, torch.float32, 1)
+            if t.shape[0] != n:
+                raise KernelError(f"linear_scan: {name} must have {n} entries")
+    if not _lib("linear_scan").lsb_linear_scan_supported(_i(key_dim)):
+        raise KernelError(f"linear_scan: key_dim {key_dim} is not supported")
+    _call("linear_scan", "lsb_linear_scan", _p(proj), _i(_dt(proj)), _ll(ld), _i(q_off), _i(k_off), _i(v_off),
+          _i(heads), _i(key_dim), _i(value_dim), _i(SCAN_GATES[gate]), _p(decay), _p(f_bias), _p(floor),
+          _i(_SCAN_ACTS[q_act]), _i(_SCAN_ACTS[k_act]), _i(_SCAN_ACTS[v_act]), _p(state), _i(state.shape[0]),
+          _p(ctx.q_start), _p(ctx.table_rows), _i(ctx.n_requests), _p(out), _stream(out))
+
+
+# --------------------------------------------------------------------- latent attention
+_PAIRINGS = {"half": 0, "adjacent": 1}
+
+
+def _check_latent_cache(cache, width: int, dtype) -> None:
+    t = _req(cache.pages, "pages", dtype, 3)
+    if t.shape[1:] != (cache.page_size, width):
+        raise KernelError(f"latent pages are {tuple(t.shape)}, expected [pages, {cache.page_size}, {width}]")
+    _req(cache.block_table, "block_table", torch.int32, 2)
+
+
+def latent_prep(down: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, q_weight: torch.Tensor,
+                kv_weight: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], rot_dims: int,
+                pairing: str, ctx, cache, cq: torch.Tensor, write: bool) -> None:
+    """Per token: cq = rmsnorm(down[:q_rank]) * q_weight; with ``write`` also the token's cache row:
+    rmsnorm(down[q_rank:q_rank + kv_rank]) * kv_weight, then the next rot_dim values rotated by the
+    token's position."""
+    _req(down, "down", torch.float32, 2)
+    _req(q_weight, "q_weight", torch.float32, 1)
+    _req(cq, "cq", dim=2)
+    T, ld = down.shape
+    if cq.shape != (T, q_rank) or q_weight.shape[0] != q_rank or ctx.n_tokens != T:
+        raise KernelError("latent_prep: cq, the weight or the step do not fit")
+    if write:
+        _req(kv_weight, "kv_weight", torch.float32, 1)
+        if ld != q_rank + kv_rank + rot_dim or kv_weight.shape[0] != kv_rank:
+            raise KernelError("latent_prep: down must hold q_rank + kv_rank + rot_dim columns")
+        if rot_dims:
+            _req(inv_freq, "inv_freq", torch.float32, 1)
+            if inv_freq.shape[0] != rot_dims // 2:
+                raise KernelError("latent_prep: inv_freq must have rot_dims / 2 entries")
+        _check_latent_cache(cache, kv_rank + rot_dim, cq.dtype)
+    elif ld < q_rank:
+        raise KernelError("latent_prep: down is narrower than q_rank")
+    _call("latent", "lsb_latent_prep", _p(down), _ll(ld), _i(T), _i(q_rank), _i(kv_rank), _i(rot_dim),
+          _p(q_weight), _p(kv_weight if write else None), _f(eps), _p(inv_freq if write else None), _i(rot_dims),
+          _i(_PAIRINGS[pairing]), _p(ctx.positions), _p(ctx.token_req), _p(ctx.table_rows),
+          _p(cache.block_table), _i(cache.block_table.shape[1]), _p(cache.pages), _i(_dt(cq)),
+          _i(cache.page_size), _i(cache.pages.shape[0]), _p(cq), _i(1 if write else 0), _stream(cq))
+
+
+def latent_query_rot(q: torch.Tensor, qf: torch.Tensor, heads: int, plain: int, rot_dim: int, kv_rank: int,
+                     inv_freq: Optional[torch.Tensor], rot_dims: int, pairing: str, ctx) -> None:
+    """qf[t, h, kv_rank:] = the last rot_dim values of head h of q[t], rotated by the token's position."""
+    _req(q, "q", torch.float32, 2)
+    _req(qf, "qf", torch.float32, 3)
+    T = q.shape[0]
+    if q.shape[1] != heads * (plain + rot_dim) or qf.shape != (T, heads, kv_rank + rot_dim):
+        raise KernelError("latent_query_rot: q or qf do not fit the sizes")
+    if rot_dims:
+        _req(inv_freq, "inv_freq", torch.float32, 1)
+    _call("latent", "lsb_latent_query_rot", _p(q), _p(qf), _i(T), _i(heads), _i(plain), _i(rot_dim), _i(kv_rank),
+          _i(rot_dims), _i(_PAIRINGS[pairing]), _p(inv_freq), _p(ctx.positions), _stream(qf))
+
+
+def batched_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[m, h, :] = a[m, h, :] @ b[h].T for every h: ``a`` [M, H, K] and ``out`` [M, H, N] may be
+    views with any row and head strides (unit stride along the last axis), ``b`` [H, N, K] is dense.
+    32-bit accumulation."""
+    for name, t in (("a", a), ("out", out)):
+        _req(t, name, dim=3, contiguous=False)
+        if t.stride(2) != 1:
+            raise KernelError(f"batched_nt: {name} needs unit stride along its last axis")
+    _req(b, "b", dim=3)
+    M, H, K = a.shape
+    N = b.shape[1]
+    if b.shape != (H, N, K) or out.shape != (M, H, N):
+        raise KernelError(f"batched_nt: a {tuple(a.shape)}, b {tuple(b.shape)}, out {tuple(out.shape)} do not fit")
+    _call("latent", "lsb_batched_nt", _p(a), _i(_dt(a)), _ll(a.stride(0)), _ll(a.stride(1)), _p(b), _i(_dt(b)),
+          _p(out), _i(_dt(out)), _ll(out.stride(0)), _ll(out.stride(1)), _i(M), _i(N), _i(K), _i(H), _stream(out))
+
+
+def latent_attention(qf: torch.Tensor, ctx, cache, kv_rank: int, rot_dim: int, scale: float,
+                     out: torch.Tensor) -> None:
+    """Causal softmax attention of this step's rows over their requests' latent cache rows:
+    scores (qf . row) * scale over the whole row, values the first kv_rank dims of the rows."""
+    _req(qf, "qf", torch.float32, 3)
+    _req(out, "out", dim=3)
+    T, H, width = qf.shape
+    if width != kv_rank + rot_dim or out.shape != (T, H, kv_rank) or ctx.n_tokens != T:
+        raise KernelError("latent_attention: qf, out or the step do not fit the sizes")
+    _check_latent_cache(cache, width, out.dtype)
+    _call("latent", "lsb_latent_attention", _p(qf), _p(cache.pages), _i(_dt(out)), _p(ctx.q_start), _p(ctx.kv_len),
+          _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(out), _i(ctx.n_requests),
+          _i(ctx.max_q_len), _i(H), _i(kv_rank), _i(rot_dim), _i(cache.page_size), _i(cache.pages.shape[0]),
+          _f(scale), _stream(out))
+
+
+# ------------------------------------------------------------------------ routed experts
+MOE_SCORES = {"sigmoid": 0, "softmax": 1}
+
+
+def moe_tile() -> int:
+    """Rows an expert's share of a step is padded to."""
+    return int(_lib("moe").lsb_moe_tile())
+
+
+def moe_route(logits: torch.Tensor, top: int, score: str, renormalize: bool, ids: torch.Tensor,
+              weights: torch.Tensor) -> None:
+    """The ``top`` experts with the largest scores per row of 32-bit ``logits`` and their scores."""
+    _req(logits, "logits", torch.float32, 2)
+    _req(ids, "ids", torch.int32, 2)
+    _req(weights, "weights", torch.float32, 2)
+    T, E = logits.shape
+    if ids.shape != (T, top) or weights.shape != (T, top) or not 0 < top <= min(E, 32):
+        raise KernelError("moe_route: ids / weights must be [tokens, top], top at most 32")
+    _call("moe", "lsb_moe_route", _p(logits), _i(T), _i(E), _i(top), _i(MOE_SCORES[score]),
+          _i(1 if renormalize else 0), _p(ids), _p(weights), _stream(ids))
+
+
+def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
+                w_down: torch.Tensor, activation: str, weight_on: str, out: torch.Tensor) -> None:
+    """out[t] = sum over k of down_e(act(gate_e u) * up_e u), e = ids[t, k], with u = weights[t, k] * x[t]
+    (``weight_on`` "input") or u = x[t] and the sum weighted ("output").  ``w_gate_up`` [E, 2F, H] has
+    rows alternating gate_i, up_i; ``w_down`` [E, H, F]."""
+    _req(x, "x", dim=2)
+    _req(ids, "ids", torch.int32, 2)
+    _req(weights, "weights", torch.float32, 2)
+    _req(w_gate_up, "w_gate_up", x.dtype, 3)
+    _req(w_down, "w_down", x.dtype, 3)
+    _req(out, "out", x.dtype, 2)
+    T, H = x.shape
+    E, F2, _ = w_gate_up.shape
+    F, top = F2 // 2, ids.shape[1]
+    if w_gate_up.shape != (E, 2 * F, H) or w_down.shape != (E, H, F) or out.shape != (T, H) \
+            or ids.shape[0] != T or weights.shape != ids.shape or weight_on not in ("input", "output"):
+        raise KernelError("moe_experts: shapes disagree")
+    tile = moe_tile()
+    cap_tiles = -(-T * top // tile) + E
+    dev = x.device
+    pos = torch.empty(T * top, dtype=torch.int32, device=dev)
+    row_token = torch.empty(cap_tiles * tile, dtype=torch.int32, device=dev)
+    row_scale = torch.empty(cap_tiles * tile, dtype=torch.float32, device=dev)
+    tile_expert = torch.empty(cap_tiles, dtype=torch.int32, device=dev)
+    hidden = torch.empty(cap_tiles * tile, F, dtype=x.dtype, device=dev)
+    y = torch.empty(cap_tiles * tile, H, dtype=torch.float32, device=dev)
+    s = _stream(out)
+    on_input = 1 if weight_on == "input" else 0
+    _call("moe", "lsb_moe_align", _p(ids), _p(weights), _i(T), _i(top), _i(E), _i(cap_tiles), _p(pos), _p(row_token),
+          _p(row_scale), _p(tile_expert), s)
+    _call("moe", "lsb_moe_up", _p(x), _i(_dt(x)), _p(row_token), _p(row_scale), _i(on_input), _p(w_gate_up),
+          _p(tile_expert), _i(cap_tiles), _p(hidden), _i(F), _i(H), _i(_activation_id(activation)), s)
+    _call("moe", "lsb_moe_down", _p(hidden), _i(_dt(x)), _p(row_token), _p(w_down), _p(tile_expert), _i(cap_tiles),
+          _p(y), _i(H), _i(F), s)
+    _call("moe", "lsb_moe_combine", _p(y), _p(pos), _p(weights), _i(1 - on_input), _i(T), _i(top), _i(H),
+          _i(cap_tiles * tile), _p(out), _i(_dt(out)), s)
+
+
 def sample(logits: torch.Tensor, params: torch.Tensor, top_k: torch.Tensor,
            prev_start: Optional[torch.Tensor], prev_tokens: Optional[torch.Tensor],
            out: torch.Tensor, work: Optional[torch.Tensor] = None) -> None:

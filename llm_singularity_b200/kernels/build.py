@@ -40,6 +40,10 @@ SOURCES: Dict[str, object] = {          # library -> its source file (or files)
     "gemm_tc": "gemm_tc.cu",
     "gemm_small": "gemm_small.cu",
     "gemm_stream": "gemm_stream.cu",
+    "rownorm": "rownorm.cu",
+    "linear_scan": "linear_scan.cu",
+    "latent": "latent.cu",
+    "moe": "moe.cu",
     "sampling": "sampling.cu",
     "random_init": "random_init.cu",
     # host code only: pools, block tables, prefix tree; scheduler

@@ -81,6 +81,10 @@ class DecoderModel:
                 part.load(per_owner[path])
         if self.spec.head.tied:
             self.head.tie(self.embedding)
+        for b in self.blocks:                       # blocks that take per-token inputs from a table
+            bind = getattr(b, "bind_embedding", None)    # the embedding holds
+            if bind is not None:
+                bind(self.embedding)
 
     # -------------------------------------------------------------------- cache
     def cache_specs(self) -> List[object]:

@@ -35,6 +35,8 @@ class PagedAttention(Part):
         if s.window is not None and s.window < 1:
             raise ValueError(f"window must be at least 1, got {s.window}")
         self.position = POSITIONS.build(s.position, rt)
+        if getattr(s.position, "pairing", "half") != "half":
+            raise ValueError("this mixer's kernels rotate dims (i, i + rotary_dim/2) together only")
         if self.position.rotary_table() is None:
             self.replayable = False          # a position encoding applied with tensor operations
         if rt.dtype == torch.bfloat16 and s.head_dim in (64, 128):

@@ -130,6 +130,36 @@ class PagedKVSpec(CacheSpec):
         return 2 * self.num_kv_heads * page_size * self.head_dim * element_size
 
 
+@dataclass
+class LatentCacheView:
+    """What a latent-attention call sees of its cache: one row per token."""
+
+    pages: torch.Tensor            # [num_pages, page_size, width]
+    block_table: torch.Tensor      # int32 [slots, max_pages]; rows picked by ctx.table_rows
+    page_size: int
+    group: int
+
+
+@dataclass(frozen=True)
+class LatentPagesSpec(CacheSpec):
+    """One row of ``width`` values per past token (a latent that keys and values of all heads
+    are made from, and whatever else the mixer keeps beside it), in the compute dtype."""
+
+    width: int
+    window: Optional[int] = None
+    paged = True
+    shareable = True
+
+    def allocate(self, rt, page_size, num_pages, slots):
+        return torch.zeros((num_pages, page_size, self.width), dtype=rt.dtype, device=rt.device)
+
+    def view(self, storage, group):
+        return LatentCacheView(storage, group.dev_table, group.page_size, group.index)
+
+    def bytes_per_page(self, page_size, element_size):
+        return page_size * self.width * element_size
+
+
 @dataclass(frozen=True)
 class StateSpec(CacheSpec):
     """Per-request state of fixed size (one tensor of ``shape`` per request), zero when a

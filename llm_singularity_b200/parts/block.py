@@ -12,7 +12,8 @@ from typing import Dict, Optional
 
 import torch
 
-from .base import FEED_FORWARDS, MIXERS, NORMS, Part, register_block
+from .base import FEED_FORWARDS, MIXERS, NORMS, ParamSpec, Part, register_block
+from .norm import StreamCopy
 
 
 @register_block("pre_norm")
@@ -66,3 +67,119 @@ class PreNormBlock(Part):
         if fold and next_norm is not None and self.ffn.folds_norm:
             return self.ffn.forward(self._input(h, self.ffn), ctx, into=(residual, *next_norm.fold()))
         return self.ffn.forward(self._input(h, self.ffn), ctx)
+
+
+class TokenSide(Part):
+    """A narrow second embedding of the token, added to the stream at the end of a block:
+    ``x += unit(W_proj (act(W_gate x) * e)) * w``, where ``e`` is this block's ``dim`` columns of the
+    table the embedding holds beside its own and ``unit`` divides by the root mean square."""
+
+    graph_safe = True
+    kernels = ("gemm", "rownorm")
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.table = None
+
+    @classmethod
+    def params(cls, spec) -> Dict[str, ParamSpec]:
+        return {"gate": ParamSpec((spec.dim, spec.hidden_size)), "proj": ParamSpec((spec.hidden_size, spec.dim)),
+                "norm": ParamSpec((spec.hidden_size,), role="vector", init="ones")}
+
+    def load(self, tensors):
+        self.w_gate = tensors["gate"].contiguous()
+        self.w_proj = tensors["proj"].contiguous()
+        self.norm = tensors["norm"]
+
+    def bind_embedding(self, embedding) -> None:
+        table = getattr(embedding, "side_weight", None)
+        if table is None or table.shape[1] < self.spec.offset + self.spec.dim:
+            raise ValueError("the embedding has no table of per-token inputs wide enough for this block")
+        self.table = table
+
+    def forward(self, residual: torch.Tensor, h: torch.Tensor, ctx) -> torch.Tensor:
+        s, ops = self.spec, self.rt.ops
+        g = ops.linear(h, self.w_gate)
+        ge = self.rt.empty(*g.shape)
+        ops.token_side_gate(g, self.table, ctx.token_ids, s.offset, s.activation, ge)
+        y = ops.linear(ge, self.w_proj)
+        out = None if self.rt.dtype == torch.float32 else self.rt.empty(*residual.shape)
+        ops.unit_add(residual, y, self.norm, s.eps, out)
+        return residual if out is None else out
+
+
+@register_block("post_norm")
+class PostNormBlock(Part):
+    """``x <- norm1(alpha x + g1 * mixer(x)); x <- norm2(alpha x + g2 * ffn(x))``, then the per-token
+    side input if the spec has one.  The sublayers read the stream itself; with ``gated_residual``
+    ``g = sigmoid(W x + b)`` of the sublayer's input multiplies its result, else g = 1.  The stream
+    is 32-bit and updated in place; each sum, its gate and the norm behind it are one kernel, which
+    also leaves the rounded copy that the next products read.  ``ffn`` None: no second step.
+
+    What it hands on is a ``StreamCopy``: nothing pending, and the copy for whoever reads next."""
+
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.mixer_norm = NORMS.build(spec.mixer_norm, rt)
+        self.mixer = MIXERS.build(spec.mixer, rt)
+        self.ffn = FEED_FORWARDS.build(spec.ffn, rt) if spec.ffn is not None else None
+        self.ffn_norm = NORMS.build(spec.ffn_norm, rt) if spec.ffn is not None else None
+        self.side = TokenSide(spec.side, rt) if spec.side is not None else None
+        for n in (self.mixer_norm, self.ffn_norm):
+            if n is not None and not hasattr(n, "scale_add_norm"):
+                raise ValueError(f"a norm of kind '{n.spec.kind}' cannot follow the sum (no scale_add_norm)")
+
+    @classmethod
+    def params(cls, spec) -> Dict[str, ParamSpec]:
+        p, H = {}, spec.hidden_size
+        if spec.gated_residual:
+            p["mixer_gate"] = ParamSpec((H, H))
+            p["mixer_gate_bias"] = ParamSpec((H,), role="vector", init="normal")
+            if spec.ffn is not None:
+                p["ffn_gate"] = ParamSpec((H, H))
+                p["ffn_gate_bias"] = ParamSpec((H,), role="vector", init="normal")
+        return p
+
+    def load(self, tensors):
+        self.gates = {k: v.contiguous() for k, v in tensors.items()}
+
+    def children(self) -> Dict[str, Part]:
+        c = {"mixer_norm": self.mixer_norm, "mixer": self.mixer}
+        if self.ffn is not None:
+            c.update(ffn_norm=self.ffn_norm, ffn=self.ffn)
+        if self.side is not None:
+            c["side"] = self.side
+        return c
+
+    def bind_embedding(self, embedding) -> None:
+        if self.side is not None:
+            self.side.bind_embedding(embedding)
+
+    def _sublayer(self, residual, h, y, norm, which):
+        gate = bias = None
+        if self.spec.gated_residual:
+            gate = self.rt.ops.linear(h, self.gates[which + "_gate"])
+            bias = self.gates[which + "_gate_bias"]
+        return norm.scale_add_norm(residual, self.spec.alpha, y, gate, bias)
+
+    def forward(self, residual: torch.Tensor, pending, ctx, cache, writes_cache: bool = True):
+        ops = self.rt.ops
+        if isinstance(pending, StreamCopy):
+            h = pending.values
+        elif pending is not None:
+            raise ValueError("a block that norms after the sum cannot take a pending delta")
+        elif self.rt.dtype == torch.float32:
+            h = residual
+        else:
+            h = self.rt.empty(*residual.shape)
+            ops.cast_rows(residual, h)
+        y = self.mixer.forward(h, ctx, cache, writes_cache)
+        h = self._sublayer(residual, h, y, self.mixer_norm, "mixer")
+        if self.ffn is not None:
+            y = self.ffn.forward(h, ctx)
+            h = self._sublayer(residual, h, y, self.ffn_norm, "ffn")
+        if self.side is not None:
+            h = self.side.forward(residual, h, ctx)
+        return StreamCopy(h)

@@ -26,10 +26,16 @@ class Embedding(Part):
 
     @classmethod
     def params(cls, spec) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((spec.vocab_size, spec.hidden_size), role="table")}
+        p = {"weight": ParamSpec((spec.vocab_size, spec.hidden_size), role="table")}
+        if getattr(spec, "side_size", 0):
+            # a second table of per-token inputs that blocks pick their columns from
+            p["side_weight"] = ParamSpec((spec.vocab_size, spec.side_size), role="table")
+        return p
 
     def load(self, tensors):
         self.weight = tensors["weight"].contiguous()
+        if "side_weight" in tensors:
+            self.side_weight = tensors["side_weight"].contiguous()
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         out = self.rt.empty(token_ids.shape[0], self.spec.hidden_size, dtype=torch.float32)

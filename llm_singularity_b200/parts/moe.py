@@ -1,0 +1,68 @@
+"""Routed feed-forward: every token is sent through ``top`` of ``num_experts`` small gated
+feed-forwards, ``down_e(act(gate_e u) * up_e u)``, no bias.
+
+The router is one product with 32-bit output; its logits become scores (sigmoid, or softmax
+over all experts), the ``top`` largest are chosen (the lower index wins a tie) and, if the spec
+says so, divided by their sum.  A score multiplies what the spec names: the expert's input
+(``u = s x``; with a gated expert that is not the same as scaling its output) or its output.
+
+The experts' matrices are stacked (``[E, 2F, H]`` with rows alternating gate_i, up_i, and
+``[E, H, F]``); a step's (token, choice) pairs are sorted by expert on the device into row
+tiles that belong to one expert each, two grouped products run over the used tiles, and the
+rows are summed back per token in the order of the token's choices.  Nothing is read back to the
+host, so a decode step launches the same kernels whatever the router decides.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .base import ParamSpec, Part, register_feed_forward
+
+
+@register_feed_forward("moe")
+class RoutedExperts(Part):
+    graph_safe = True
+    kernels = ("gemm", "moe")
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        s = spec
+        if not 0 < s.top <= s.num_experts:
+            raise ValueError(f"top {s.top} of {s.num_experts} experts")
+        if s.score not in ("sigmoid", "softmax") or s.weight_on not in ("input", "output"):
+            raise ValueError(f"score '{s.score}' / weight_on '{s.weight_on}' is not known")
+        known = getattr(rt.ops, "ACTIVATIONS", None)
+        if known is not None and s.activation not in known:
+            raise ValueError(f"activation '{s.activation}' is not implemented")
+
+    @classmethod
+    def params(cls, spec) -> Dict[str, ParamSpec]:
+        H, F = spec.hidden_size, spec.expert_size
+        p = {"router": ParamSpec((spec.num_experts, H))}
+        for e in range(spec.num_experts):
+            p[f"e{e}.gate"] = ParamSpec((F, H))
+            p[f"e{e}.up"] = ParamSpec((F, H))
+            p[f"e{e}.down"] = ParamSpec((H, F))
+        return p
+
+    def load(self, tensors):
+        s = self.spec
+        E, F, H = s.num_experts, s.expert_size, s.hidden_size
+        self.w_router = tensors["router"].contiguous()
+        # rows 2i, 2i + 1 of an expert = gate_i, up_i
+        self.w_gate_up = torch.stack(
+            [torch.stack([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=1).reshape(2 * F, H) for e in range(E)]
+        ).contiguous()
+        self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(E)]).contiguous()
+
+    def forward(self, x, ctx):
+        s, ops, T = self.spec, self.rt.ops, x.shape[0]
+        logits = ops.linear(x, self.w_router, out_dtype=torch.float32)
+        ids = self.rt.empty(T, s.top, dtype=torch.int32)
+        weights = self.rt.empty(T, s.top, dtype=torch.float32)
+        ops.moe_route(logits, s.top, s.score, s.renormalize, ids, weights)
+        out = self.rt.empty(T, s.hidden_size)
+        ops.moe_experts(x, ids, weights, self.w_gate_up, self.w_down, s.activation, s.weight_on, out)
+        return out

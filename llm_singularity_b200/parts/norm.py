@@ -43,3 +43,66 @@ class RMSNorm(Part):
         out = self.rt.empty(rows.shape[0], residual.shape[1])
         self.rt.ops.gather_add_rmsnorm(residual, delta, rows, self.weight, self.spec.eps, out)
         return out
+
+
+class StreamCopy:
+    """What a block that norms after the sum hands to the next block in place of a pending delta:
+    nothing is left to add, and ``values`` is the residual stream rounded to the compute dtype
+    (the stream itself where the compute dtype is 32-bit), ready to be a product's operand."""
+
+    __slots__ = ("values",)
+
+    def __init__(self, values: torch.Tensor):
+        self.values = values
+
+
+@register_norm("group_rmsnorm")
+class GroupRMSNorm(Part):
+    """RMS norm in ``groups`` equal consecutive parts of the vector, one weight over the whole:
+    ``y[g] = x[g] / sqrt(mean(x[g]^2) + eps) * w[g]``, all in 32-bit.
+
+    Besides the interface of every norm (``add_norm``: the sum stays in the stream, for
+    arrangements that norm before a sublayer) it has ``scale_add_norm`` for arrangements that norm
+    after the sum: the stream itself becomes ``norm(alpha * x + gate * delta)``."""
+
+    graph_safe = True
+    kernels = ("rownorm",)
+
+    @classmethod
+    def params(cls, spec) -> Dict[str, ParamSpec]:
+        return {"weight": ParamSpec((spec.size,), role="vector", init="ones")}
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        if spec.groups <= 0 or spec.size % spec.groups:
+            raise ValueError(f"{spec.groups} groups do not divide a vector of {spec.size}")
+
+    def load(self, tensors):
+        self.weight = tensors["weight"]
+
+    def _copy(self, residual):
+        return None if self.rt.dtype == torch.float32 else self.rt.empty(*residual.shape)
+
+    def add_norm(self, residual: torch.Tensor, delta) -> torch.Tensor:
+        if isinstance(delta, StreamCopy):
+            delta = None
+        out = self.rt.empty(*residual.shape)
+        self.rt.ops.post_group_norm(residual, delta, self.weight, self.spec.eps, self.spec.groups, 1.0, out,
+                                    keep_sum=True)
+        return out
+
+    def scale_add_norm(self, residual: torch.Tensor, alpha: float, delta: torch.Tensor,
+                       gate: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """residual <- norm(alpha * residual + delta * sigmoid(gate + gate_bias)) in place; returns the
+        stream as a product's operand (a rounded copy, or the stream itself in 32-bit)."""
+        out = self._copy(residual)
+        self.rt.ops.post_group_norm(residual, delta, self.weight, self.spec.eps, self.spec.groups, alpha, out,
+                                    gate=gate, gate_bias=gate_bias, dtype=self.rt.dtype)
+        return residual if out is None else out
+
+    def gather_add_norm(self, residual: torch.Tensor, delta, rows: torch.Tensor) -> torch.Tensor:
+        if delta is not None and not isinstance(delta, StreamCopy):
+            raise ValueError("the group norm gathers rows of a stream that has nothing pending")
+        out = self.rt.empty(rows.shape[0], residual.shape[1])
+        self.rt.ops.gather_group_norm(residual, rows, self.weight, self.spec.eps, self.spec.groups, out)
+        return out

@@ -59,8 +59,10 @@ def read_config_json(model_dir: str) -> dict:
 
 def architecture_of(config_dict: dict) -> Architecture:
     archs = config_dict.get("architectures")
+    if archs is None and isinstance(config_dict.get("architecture"), str):
+        archs = [config_dict["architecture"]]          # some configurations name one class, as a string
     if not archs or not isinstance(archs, list):
-        raise UnknownArchitecture("config.json: 'architectures' must name the model class")
+        raise UnknownArchitecture("config.json: 'architectures' (or 'architecture') must name the model class")
     return get_architecture(archs[0])
 
 
@@ -73,6 +75,8 @@ def load_config(model_dir: str):
 def _register_builtin() -> None:
     from .config.llama import LlamaConfig
     register_architecture(LlamaConfig.architecture, LlamaConfig)
+    from .config.ridotar import RidotarConfig
+    register_architecture(RidotarConfig.architecture, RidotarConfig)
 
 
 _register_builtin()
