@@ -154,6 +154,12 @@ struct GemmParams {
                                   // The output then has half as many columns: silu(gate) * up.
     int static_operand;           // 1: P holds weights, 2: Q does (loaded before the PDL wait)
     void* out;                    // bf16 or float
+    // Grouped products (routed experts): Q stacks one matrix of `group_rows` rows per group, and
+    // tile_group[i0 / 128] names the group whose matrix the 128-row tile of P is multiplied with
+    // (-1: the tile is unused).  Null: one matrix for all tiles.  The list is written by a kernel
+    // earlier in the stream, so a block reads it only after the wait on that kernel.
+    const int* tile_group;
+    int group_rows;
 };
 
 template <int BN>
@@ -401,6 +407,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     const int nkb = max(0, kb1 - kb0);
 
     lsb_pdl_launch_dependents();
+    int jq0 = j0;                                  // first row of this tile's Q operand
+    if (prm.tile_group) {
+        lsb_pdl_wait();
+        const int g = prm.tile_group[blockIdx.x];
+        if (g < 0) return;                         // (before any barrier or tensor memory exists)
+        jq0 = j0 + g * prm.group_rows;
+    }
     const int pre = min(nkb, STAGES);
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -415,7 +428,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             unsigned char* st = stages + (size_t)kb * L::kStageBytes;
             mbar_expect_tx(&full[kb], L::kStageBytes);
             if (prm.static_operand == 1) tma_load_2d(st, &map_p, &full[kb], (kb0 + kb) * kBK, i0);
-            else tma_load_2d(st + L::kPBytes, &map_q, &full[kb], (kb0 + kb) * kBK, j0);
+            else tma_load_2d(st + L::kPBytes, &map_q, &full[kb], (kb0 + kb) * kBK, jq0);
         }
     }
     if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
@@ -430,7 +443,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             lsb_pdl_wait();
             for (int kb = 0; kb < pre; ++kb) {
                 unsigned char* st = stages + (size_t)kb * L::kStageBytes;
-                if (prm.static_operand == 1) tma_load_2d(st + L::kPBytes, &map_q, &full[kb], (kb0 + kb) * kBK, j0);
+                if (prm.static_operand == 1) tma_load_2d(st + L::kPBytes, &map_q, &full[kb], (kb0 + kb) * kBK, jq0);
                 else tma_load_2d(st, &map_p, &full[kb], (kb0 + kb) * kBK, i0);
             }
             int issued = pre;
@@ -440,7 +453,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 mbar_expect_tx(&full[s], L::kStageBytes);
                 unsigned char* st = stages + (size_t)s * L::kStageBytes;
                 tma_load_2d(st, &map_p, &full[s], (kb0 + kb) * kBK, i0);
-                tma_load_2d(st + L::kPBytes, &map_q, &full[s], (kb0 + kb) * kBK, j0);
+                tma_load_2d(st + L::kPBytes, &map_q, &full[s], (kb0 + kb) * kBK, jq0);
                 issued = kb + 1;
             }
             // copies still in flight must land before the block may exit
@@ -940,6 +953,8 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
     prm.out_f32 = out_f32;
     prm.out = out;
     prm.act = swiglu;
+    prm.tile_group = nullptr;
+    prm.group_rows = 0;
     const int sms = num_sms();
     CUtensorMap mp, mq;
     int rc;
@@ -1019,3 +1034,41 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
     return rc;
 }
 
+
+
+// Grouped form for routed experts: x [M, K] holds row tiles of 128 that belong to one group each
+// (tile_group[M / 128], device memory, -1 for an unused tile), w stacks `groups` matrices [N, K];
+// out[m] = x[m] w[group of m's tile]^T, gated as above if swiglu.  M is a multiple of 128.
+LSB_API int lsb_gemm_tc_grouped(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
+                                int groups, const int* tile_group, int swiglu, cudaStream_t stream) {
+    if (M <= 0) return 0;
+    if (!lsb_gemm_tc_supported(x, w, M, N, K) || M % kBM || groups <= 0 || !tile_group) return (int)cudaErrorInvalidValue;
+    if ((swiglu && (N % 2)) || swiglu < 0 || swiglu > LSB_ACT_NONE) return (int)cudaErrorInvalidValue;
+    if ((long long)groups * N > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
+    const int n_out = swiglu ? N / 2 : N;
+    GemmParams prm;
+    prm.K = K;
+    prm.num_kb = (K + kBK - 1) / kBK;
+    prm.kb_per_split = prm.num_kb;
+    prm.splits = 1;
+    prm.out_f32 = out_f32;
+    prm.out = out;
+    prm.act = swiglu;
+    prm.tile_group = tile_group;
+    prm.group_rows = N;
+    prm.rows_p = M; prm.rows_q = N; prm.ldc_i = n_out; prm.ldc_j = 1;
+    prm.swiglu = swiglu ? 1 : 0;
+    prm.static_operand = 2;
+    const int bn = N >= 256 ? 256 : N > 64 ? 128 : 64;
+    CUtensorMap mp, mq;
+    int rc;
+    if ((rc = make_map(&mp, x, M, K, kBM))) return rc;
+    if ((rc = make_map(&mq, w, groups * N, K, bn))) return rc;
+    dim3 grid(M / kBM, (N + bn - 1) / bn, 1);
+    if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+    switch (bn) {
+        case 64: return launch<64, 4>(mp, mq, prm, grid, stream);
+        case 128: return launch<128, 6>(mp, mq, prm, grid, stream);
+        default: return launch<256, 4>(mp, mq, prm, grid, stream);
+    }
+}

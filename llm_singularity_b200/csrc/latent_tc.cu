@@ -1,0 +1,255 @@
+// Attention over a cached latent on the tensor cores (bfloat16 cache, warp-level MMA).
+//
+// Every head of a token reads the same cache rows (see latent.cu), so the (token, head) pairs of
+// a request are the rows of one matrix: a block takes 64 of them, Q [64, kv_rank + rot_dim], and
+// walks the request's keys in tiles of 64 rows of the cache.  S = Q K^T over the whole row width,
+// O += P V over the first kv_rank columns of the same tile.  The softmax is done in two passes
+// over the keys: the first finds every row's maximum and sum, the second forms the normalised
+// weights and accumulates O, so the accumulators (fragments, kept in registers) never have to be
+// rescaled row by row.  The price is a second Q K^T; what it buys is that a row's result does not
+// depend on the order in which maxima were met.
+//
+// For steps of single tokens the keys of a request are split over `splits` blocks (grid.z), each
+// writing a normalised partial result with its maximum and sum; a second kernel merges them.
+//
+// Scores, maxima, sums and weights are 32-bit; Q and P are rounded to bfloat16 as MMA operands.
+#include "common.cuh"
+
+#include <float.h>
+#include <mma.h>
+
+using namespace nvcuda;
+typedef __nv_bfloat16 bf16;
+
+LSB_DEFINE_STATUS()
+
+constexpr int kRows = 64;               // (token, head) rows per block
+constexpr int kKeys = 64;               // keys per tile
+constexpr int kLtThreads = 256;         // 8 warps: 4 row groups x 2 column halves
+constexpr int kMaxFrag = 16;            // 16-column fragments of O per warp: kv_rank <= 2 * 16 * 16
+constexpr int kLdS = kKeys + 4;         // floats per row of the score tile
+constexpr int kLdP = kKeys + 8;         // bfloat16 per row of the weight tile
+
+__global__ void __launch_bounds__(kLtThreads, 1)
+latent_attention_tc_kernel(const float* __restrict__ qf, const bf16* __restrict__ pages,
+                           const int* __restrict__ q_start, const int* __restrict__ kv_len_arr,
+                           const int* __restrict__ table_rows, const int* __restrict__ block_table,
+                           int table_stride, bf16* __restrict__ out, float* __restrict__ part_o,
+                           float* __restrict__ part_ml, int heads, int kv_rank, int rot_dim,
+                           int page_size, int num_pages, float scale, int splits) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int Dk = kv_rank + rot_dim, ldk = Dk + 8;
+    bf16* Qs = reinterpret_cast<bf16*>(smem);                 // [64][ldk]
+    bf16* Ks = Qs + kRows * ldk;                              // [64][ldk]
+    float* Ss = reinterpret_cast<float*>(Ks + kKeys * ldk);   // [64][kLdS]
+    bf16* Ps = reinterpret_cast<bf16*>(Ss + kRows * kLdS);    // [64][kLdP]
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int r = blockIdx.y, split = blockIdx.z;
+    const int qs = q_start[r];
+    const int q_len = q_start[r + 1] - qs;
+    const int n_rows = q_len * heads;
+    const int row0 = blockIdx.x * kRows;
+    if (row0 >= n_rows) return;
+    const int kv_len = kv_len_arr[r];
+    const int first_pos = kv_len - q_len;
+    const int last_row = min(row0 + kRows, n_rows) - 1;
+    const int n_keys = first_pos + last_row / heads + 1;      // keys any row of this block may see
+    int per = (n_keys + splits - 1) / splits;
+    per = (per + kKeys - 1) / kKeys * kKeys;
+    const int kbeg = split * per, kend = min(n_keys, kbeg + per);
+    const int* bt = block_table + (size_t)table_rows[r] * table_stride;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // Q: rows of the block are consecutive rows of qf [(token, head), Dk]
+    const float* qsrc = qf + ((size_t)qs * heads + row0) * Dk;
+    for (int i = tid; i < kRows * Dk; i += kLtThreads) {
+        const int row = i / Dk, d = i % Dk;
+        Qs[row * ldk + d] = __float2bfloat16_rn(row0 + row < n_rows ? qsrc[(size_t)row * Dk + d] : 0.f);
+    }
+    // the softmax's view: four neighbouring lanes share a row, 16 keys of the tile each
+    const int srow = tid >> 2, squarter = tid & 3;
+    const int p_row = row0 + srow < n_rows ? first_pos + (row0 + srow) / heads : -1;
+    float m = -FLT_MAX, l = 0.f, inv_l = 0.f;
+
+    const int mi = warp & 3, half = warp >> 2;
+    const int nf = kv_rank / 32;                              // fragments of O per warp
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[kMaxFrag];
+#pragma unroll
+    for (int f = 0; f < kMaxFrag; ++f) wmma::fill_fragment(acc[f], 0.f);
+
+    for (int pass = 0; pass < 2; ++pass) {
+        for (int k0 = kbeg; k0 < kend; k0 += kKeys) {
+            __syncthreads();                                  // the tile before is no longer read
+            const int chunks = Dk / 8;                        // 16-byte pieces of a cache row
+            for (int i = tid; i < kKeys * chunks; i += kLtThreads) {
+                const int j = i / chunks, c = i % chunks;
+                const int kj = k0 + j;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (kj < kend) {
+                    const int page = bt[kj / page_size];
+                    if (page < 0 || page >= num_pages) lsb_set_status(LSB_BAD_PAGE);
+                    else v = *reinterpret_cast<const uint4*>(pages + ((size_t)page * page_size + kj % page_size) * Dk + c * 8);
+                }
+                *reinterpret_cast<uint4*>(Ks + j * ldk + c * 8) = v;
+            }
+            __syncthreads();
+            {   // S = Q K^T: this warp's 16 rows x 32 keys
+                wmma::fragment<wmma::accumulator, 16, 16, 16, float> s0, s1;
+                wmma::fill_fragment(s0, 0.f);
+                wmma::fill_fragment(s1, 0.f);
+                for (int k = 0; k < Dk; k += 16) {
+                    wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
+                    wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b0, b1;
+                    wmma::load_matrix_sync(a, Qs + mi * 16 * ldk + k, ldk);
+                    wmma::load_matrix_sync(b0, Ks + (half * 32) * ldk + k, ldk);
+                    wmma::load_matrix_sync(b1, Ks + (half * 32 + 16) * ldk + k, ldk);
+                    wmma::mma_sync(s0, a, b0, s0);
+                    wmma::mma_sync(s1, a, b1, s1);
+                }
+                wmma::store_matrix_sync(Ss + mi * 16 * kLdS + half * 32, s0, kLdS, wmma::mem_row_major);
+                wmma::store_matrix_sync(Ss + mi * 16 * kLdS + half * 32 + 16, s1, kLdS, wmma::mem_row_major);
+            }
+            __syncthreads();
+            const float* srow_p = Ss + srow * kLdS + squarter * 16;
+            if (pass == 0) {
+                float tmax = -FLT_MAX;
+                float sv[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const int kj = k0 + squarter * 16 + c;
+                    sv[c] = (kj <= p_row && kj < kend) ? srow_p[c] * scale : -FLT_MAX;
+                    tmax = fmaxf(tmax, sv[c]);
+                }
+                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+                const float m_new = fmaxf(m, tmax);
+                float sum = 0.f;
+#pragma unroll
+                for (int c = 0; c < 16; ++c) sum += sv[c] > -FLT_MAX ? expf(sv[c] - m_new) : 0.f;
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                l = l * expf(m - m_new) + sum;                // m == -FLT_MAX at first: exp(-huge) = 0
+                m = m_new;
+            } else {
+                bf16* prow = Ps + srow * kLdP + squarter * 16;
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const int kj = k0 + squarter * 16 + c;
+                    const float p = (kj <= p_row && kj < kend) ? expf(srow_p[c] * scale - m) * inv_l : 0.f;
+                    prow[c] = __float2bfloat16_rn(p);
+                }
+                __syncthreads();
+                // O += P V: this warp's 16 rows x its half of the value columns
+                wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> pa[kKeys / 16];
+#pragma unroll
+                for (int kk = 0; kk < kKeys / 16; ++kk)
+                    wmma::load_matrix_sync(pa[kk], Ps + mi * 16 * kLdP + kk * 16, kLdP);
+#pragma unroll
+                for (int f = 0; f < kMaxFrag; ++f) {
+                    if (f < nf) {
+                        const int col = half * (kv_rank / 2) + f * 16;
+#pragma unroll
+                        for (int kk = 0; kk < kKeys / 16; ++kk) {
+                            wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> vb;
+                            wmma::load_matrix_sync(vb, Ks + kk * 16 * ldk + col, ldk);
+                            wmma::mma_sync(acc[f], pa[kk], vb, acc[f]);
+                        }
+                    }
+                }
+            }
+        }
+        if (pass == 0) inv_l = l > 0.f ? 1.f / l : 0.f;
+    }
+    __syncthreads();                                          // Ss is free: it becomes the staging area
+    if (splits > 1 && squarter == 0 && row0 + srow < n_rows) {
+        float* ml = part_ml + (((size_t)qs * heads + row0 + srow) * splits + split) * 2;
+        ml[0] = m;
+        ml[1] = l;
+    }
+    float* stage = Ss + warp * 256;
+#pragma unroll
+    for (int f = 0; f < kMaxFrag; ++f) {
+        if (f < nf) {
+            wmma::store_matrix_sync(stage, acc[f], 16, wmma::mem_row_major);
+            __syncwarp();
+            const int row = lane >> 1, c0 = (lane & 1) * 8;
+            const int grow = row0 + mi * 16 + row;
+            const int col = half * (kv_rank / 2) + f * 16 + c0;
+            if (grow < n_rows) {
+                const float* src = stage + row * 16 + c0;
+                if (splits > 1) {
+                    float* dst = part_o + (((size_t)qs * heads + grow) * splits + split) * kv_rank + col;
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) dst[x] = src[x];
+                } else {
+                    bf16* dst = out + ((size_t)qs * heads + grow) * kv_rank + col;
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) dst[x] = __float2bfloat16_rn(src[x]);
+                }
+            }
+            __syncwarp();
+        }
+    }
+}
+
+// out[row] = sum over splits of w_s part_o[row, s], w_s = l_s e^(m_s - M) / sum of the same
+__global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    bf16* __restrict__ out, int splits, int kv_rank) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const size_t row = blockIdx.x;
+    const float* ml = part_ml + row * splits * 2;
+    float M = -FLT_MAX;
+    for (int s = 0; s < splits; ++s)
+        if (ml[2 * s + 1] > 0.f) M = fmaxf(M, ml[2 * s]);
+    float total = 0.f;
+    for (int s = 0; s < splits; ++s)
+        if (ml[2 * s + 1] > 0.f) total += ml[2 * s + 1] * expf(ml[2 * s] - M);
+    const float inv = total > 0.f ? 1.f / total : 0.f;
+    for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ls = ml[2 * s + 1];
+            if (ls > 0.f) acc += ls * expf(ml[2 * s] - M) * inv * part_o[(row * splits + s) * kv_rank + d];
+        }
+        out[row * kv_rank + d] = __float2bfloat16_rn(acc);
+    }
+}
+
+static size_t latent_tc_smem(int kv_rank, int rot_dim) {
+    const size_t ldk = kv_rank + rot_dim + 8;
+    return 2 * kRows * ldk * sizeof(bf16) + kRows * kLdS * sizeof(float) + kRows * kLdP * sizeof(bf16);
+}
+
+LSB_API int lsb_latent_attention_tc_supported(int kv_rank, int rot_dim) {
+    return kv_rank > 0 && kv_rank % 32 == 0 && kv_rank <= 32 * kMaxFrag && rot_dim >= 0 && rot_dim % 16 == 0 &&
+           latent_tc_smem(kv_rank, rot_dim) <= 200 * 1024;
+}
+
+// part_o [tokens * heads, splits, kv_rank] and part_ml [tokens * heads, splits, 2] are needed when
+// splits > 1 (steps of single tokens); out [tokens, heads, kv_rank] bfloat16.
+LSB_API int lsb_latent_attention_tc(const float* qf, const void* pages, const int* q_start, const int* kv_len,
+                                    const int* table_rows, const int* block_table, int table_stride,
+                                    void* out, float* part_o, float* part_ml, int n_requests, int max_q_len,
+                                    int n_tokens, int heads, int kv_rank, int rot_dim, int page_size,
+                                    int num_pages, float scale, int splits, cudaStream_t stream) {
+    if (n_requests <= 0 || max_q_len <= 0) return 0;
+    if (!lsb_latent_attention_tc_supported(kv_rank, rot_dim) || heads <= 0 || n_requests > 65535 || splits < 1 ||
+        splits > 65535 || (splits > 1 && (!part_o || !part_ml)))
+        return (int)cudaErrorInvalidValue;
+    static int configured = -1;
+    const size_t smem = latent_tc_smem(kv_rank, rot_dim);
+    if (configured < 0)
+        configured = (int)cudaFuncSetAttribute(latent_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               200 * 1024);
+    if (configured) return configured;
+    const long long rows = (long long)max_q_len * heads;
+    dim3 grid((unsigned)((rows + kRows - 1) / kRows), n_requests, splits);
+    int rc = lsb_launch(latent_attention_tc_kernel, grid, dim3(kLtThreads), smem, stream, 1, qf, (const bf16*)pages,
+                        q_start, kv_len, table_rows, block_table, table_stride, (bf16*)out, part_o, part_ml, heads,
+                        kv_rank, rot_dim, page_size, num_pages, scale, splits);
+    if (rc || splits == 1) return rc;
+    return lsb_launch(latent_merge_kernel, dim3((unsigned)((long long)n_tokens * heads)), dim3(128), 0, stream, 1,
+                      (const float*)part_o, (const float*)part_ml, (bf16*)out, splits, kv_rank);
+}

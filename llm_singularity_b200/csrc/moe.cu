@@ -77,7 +77,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int n_tokens,
 
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int n, int top, int E,
-                 int cap_tiles, int* __restrict__ pos, int* __restrict__ row_token,
+                 int cap_tiles, int tile, int* __restrict__ pos, int* __restrict__ row_token,
                  float* __restrict__ row_scale, int* __restrict__ tile_expert) {
     extern __shared__ int shi[];
     int* counts = shi;                  // E
@@ -85,7 +85,7 @@ moe_align_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
     for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
-    for (int i = threadIdx.x; i < cap_tiles * kTile; i += blockDim.x) { row_token[i] = -1; row_scale[i] = 0.f; }
+    for (int i = threadIdx.x; i < cap_tiles * tile; i += blockDim.x) { row_token[i] = -1; row_scale[i] = 0.f; }
     for (int i = threadIdx.x; i < cap_tiles; i += blockDim.x) tile_expert[i] = -1;
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -98,19 +98,19 @@ moe_align_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int
         int at = 0;
         for (int e = 0; e < E; ++e) {
             starts[e] = at;
-            at += (counts[e] + kTile - 1) / kTile * kTile;
+            at += (counts[e] + tile - 1) / tile * tile;
         }
         starts[E] = at;
     }
     __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x)
-        for (int tile = starts[e] / kTile; tile < starts[e + 1] / kTile && tile < cap_tiles; ++tile)
-            tile_expert[tile] = e;
+        for (int ti = starts[e] / tile; ti < starts[e + 1] / tile && ti < cap_tiles; ++ti)
+            tile_expert[ti] = e;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         if (pos[i] < 0) continue;
         const int p = starts[ids[i]] + pos[i];
         pos[i] = p;
-        if (p < cap_tiles * kTile) { row_token[p] = i / top; row_scale[p] = wts[i]; }
+        if (p < cap_tiles * tile) { row_token[p] = i / top; row_scale[p] = wts[i]; }
     }
 }
 
@@ -176,7 +176,19 @@ moe_gemm_kernel(const T* __restrict__ A, const int* __restrict__ row_token,
 }
 
 template <typename T>
-__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos,
+__global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ row_token,
+                                  const float* __restrict__ row_scale, int on_input, int n, T* __restrict__ rows) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const size_t r = blockIdx.x;
+    const int tok = row_token[r];
+    const float sc = on_input ? row_scale[r] : 1.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        rows[r * n + i] = tok >= 0 ? lsb_from_float<T>(sc * lsb_to_float(x[(size_t)tok * n + i])) : lsb_from_float<T>(0.f);
+}
+
+template <typename T, typename TY>
+__global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ pos,
                                    const float* __restrict__ wts, int on_output, int top, int n,
                                    int capacity, T* __restrict__ out) {
     lsb_pdl_launch_dependents();
@@ -187,7 +199,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
         for (int k = 0; k < top; ++k) {
             const int p = pos[t * top + k];
             if (p < 0 || p >= capacity) continue;
-            const float v = y[(size_t)p * n + i];
+            const float v = lsb_to_float(y[(size_t)p * n + i]);
             s += on_output ? wts[t * top + k] * v : v;
         }
         out[t * n + i] = lsb_from_float<T>(s);
@@ -206,13 +218,23 @@ LSB_API int lsb_moe_route(const float* logits, int n_tokens, int E, int top, int
 }
 
 LSB_API int lsb_moe_align(const int* ids, const float* wts, int n_tokens, int top, int E, int cap_tiles,
-                          int* pos, int* row_token, float* row_scale, int* tile_expert,
+                          int tile, int* pos, int* row_token, float* row_scale, int* tile_expert,
                           cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const long long n = (long long)n_tokens * top;
-    if (E <= 0 || E > 8192 || cap_tiles < (n + kTile - 1) / kTile + E) return (int)cudaErrorInvalidValue;
+    if (E <= 0 || E > 8192 || tile <= 0 || cap_tiles < (n + tile - 1) / tile + E) return (int)cudaErrorInvalidValue;
     return lsb_launch(moe_align_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), stream, 1,
-                      ids, wts, (int)n, top, E, cap_tiles, pos, row_token, row_scale, tile_expert);
+                      ids, wts, (int)n, top, E, cap_tiles, tile, pos, row_token, row_scale, tile_expert);
+}
+
+// rows[r] = T(scale[r] * x[row_token[r]]) (zeros in the padding): the operand of the grouped
+// tensor-core product, which wants its rows in place
+LSB_API int lsb_moe_gather(const void* x, int dtype, const int* row_token, const float* row_scale, int on_input,
+                           int capacity, int n, void* rows, cudaStream_t stream) {
+    if (capacity <= 0) return 0;
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(moe_gather_kernel<T>, dim3(capacity), dim3(128), 0, stream, 1,
+                                                (const T*)x, row_token, row_scale, on_input, n, (T*)rows));
+    return 0;
 }
 
 LSB_API int lsb_moe_up(const void* x, int dtype, const int* row_token, const float* row_scale, int on_input,
@@ -239,10 +261,17 @@ LSB_API int lsb_moe_down(const void* h, int dtype, const int* row_token, const v
     return 0;
 }
 
-LSB_API int lsb_moe_combine(const float* y, const int* pos, const float* wts, int on_output, int n_tokens,
-                            int top, int n, int capacity, void* out, int dtype, cudaStream_t stream) {
+// y_same: the expert rows are stored in the output's type (the tensor-core path), else 32-bit
+LSB_API int lsb_moe_combine(const void* y, int y_same, const int* pos, const float* wts, int on_output,
+                            int n_tokens, int top, int n, int capacity, void* out, int dtype,
+                            cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(moe_combine_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, 1,
-                                                y, pos, wts, on_output, top, n, capacity, (T*)out));
+    LSB_DISPATCH_DTYPE(dtype, {
+        if (y_same)
+            return lsb_launch(moe_combine_kernel<T, T>, dim3(n_tokens), dim3(256), 0, stream, 1, (const T*)y, pos,
+                              wts, on_output, top, n, capacity, (T*)out);
+        return lsb_launch(moe_combine_kernel<T, float>, dim3(n_tokens), dim3(256), 0, stream, 1, (const float*)y,
+                          pos, wts, on_output, top, n, capacity, (T*)out);
+    });
     return 0;
 }

@@ -918,6 +918,7 @@ def linear_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: i
 
 # --------------------------------------------------------------------- latent attention
 _PAIRINGS = {"half": 0, "adjacent": 1}
+LATENT_TENSOR_CORES = True      # bfloat16 latent attention on warp-level MMA (csrc/latent_tc.cu)
 
 
 def _check_latent_cache(cache, width: int, dtype) -> None:
@@ -998,6 +999,22 @@ def latent_attention(qf: torch.Tensor, ctx, cache, kv_rank: int, rot_dim: int, s
     if width != kv_rank + rot_dim or out.shape != (T, H, kv_rank) or ctx.n_tokens != T:
         raise KernelError("latent_attention: qf, out or the step do not fit the sizes")
     _check_latent_cache(cache, width, out.dtype)
+    if LATENT_TENSOR_CORES and out.dtype == torch.bfloat16 and \
+            _lib("latent_tc").lsb_latent_attention_tc_supported(_i(kv_rank), _i(rot_dim)):
+        # 64 (token, head) rows a block; steps of single tokens split each request's keys over
+        # blocks so that the SMs are busy (a function of the batch alone: a captured launch stays
+        # valid as the sequences grow)
+        splits, part_o, part_ml = 1, None, None
+        if ctx.max_q_len == 1:
+            splits = max(1, min(32, num_sms(qf.device) // (ctx.n_requests * -(-H // 64))))
+        if splits > 1:
+            part_o = torch.empty(T * H * splits * kv_rank, dtype=torch.float32, device=qf.device)
+            part_ml = torch.empty(T * H * splits * 2, dtype=torch.float32, device=qf.device)
+        _call("latent_tc", "lsb_latent_attention_tc", _p(qf), _p(cache.pages), _p(ctx.q_start), _p(ctx.kv_len),
+              _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(out), _p(part_o),
+              _p(part_ml), _i(ctx.n_requests), _i(ctx.max_q_len), _i(T), _i(H), _i(kv_rank), _i(rot_dim),
+              _i(cache.page_size), _i(cache.pages.shape[0]), _f(scale), _i(splits), _stream(out))
+        return
     _call("latent", "lsb_latent_attention", _p(qf), _p(cache.pages), _i(_dt(out)), _p(ctx.q_start), _p(ctx.kv_len),
           _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(out), _i(ctx.n_requests),
           _i(ctx.max_q_len), _i(H), _i(kv_rank), _i(rot_dim), _i(cache.page_size), _i(cache.pages.shape[0]),
@@ -1006,6 +1023,7 @@ def latent_attention(qf: torch.Tensor, ctx, cache, kv_rank: int, rot_dim: int, s
 
 # ------------------------------------------------------------------------ routed experts
 MOE_SCORES = {"sigmoid": 0, "softmax": 1}
+MOE_TENSOR_CORES = True         # bfloat16 experts on the grouped tcgen05 product
 
 
 def moe_tile() -> int:
@@ -1043,7 +1061,10 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     if w_gate_up.shape != (E, 2 * F, H) or w_down.shape != (E, H, F) or out.shape != (T, H) \
             or ids.shape[0] != T or weights.shape != ids.shape or weight_on not in ("input", "output"):
         raise KernelError("moe_experts: shapes disagree")
-    tile = moe_tile()
+    # bfloat16 with TMA-friendly sizes: rows gathered in place, two grouped tcgen05 products over
+    # 128-row tiles; anything else (32-bit, odd sizes): the plain grouped kernels over 32-row tiles
+    tc = MOE_TENSOR_CORES and x.dtype == torch.bfloat16 and H % 8 == 0 and F % 8 == 0
+    tile = 128 if tc else moe_tile()
     cap_tiles = -(-T * top // tile) + E
     dev = x.device
     pos = torch.empty(T * top, dtype=torch.int32, device=dev)
@@ -1051,17 +1072,27 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     row_scale = torch.empty(cap_tiles * tile, dtype=torch.float32, device=dev)
     tile_expert = torch.empty(cap_tiles, dtype=torch.int32, device=dev)
     hidden = torch.empty(cap_tiles * tile, F, dtype=x.dtype, device=dev)
-    y = torch.empty(cap_tiles * tile, H, dtype=torch.float32, device=dev)
+    y = torch.empty(cap_tiles * tile, H, dtype=x.dtype if tc else torch.float32, device=dev)
     s = _stream(out)
     on_input = 1 if weight_on == "input" else 0
-    _call("moe", "lsb_moe_align", _p(ids), _p(weights), _i(T), _i(top), _i(E), _i(cap_tiles), _p(pos), _p(row_token),
-          _p(row_scale), _p(tile_expert), s)
-    _call("moe", "lsb_moe_up", _p(x), _i(_dt(x)), _p(row_token), _p(row_scale), _i(on_input), _p(w_gate_up),
-          _p(tile_expert), _i(cap_tiles), _p(hidden), _i(F), _i(H), _i(_activation_id(activation)), s)
-    _call("moe", "lsb_moe_down", _p(hidden), _i(_dt(x)), _p(row_token), _p(w_down), _p(tile_expert), _i(cap_tiles),
-          _p(y), _i(H), _i(F), s)
-    _call("moe", "lsb_moe_combine", _p(y), _p(pos), _p(weights), _i(1 - on_input), _i(T), _i(top), _i(H),
-          _i(cap_tiles * tile), _p(out), _i(_dt(out)), s)
+    _call("moe", "lsb_moe_align", _p(ids), _p(weights), _i(T), _i(top), _i(E), _i(cap_tiles), _i(tile), _p(pos),
+          _p(row_token), _p(row_scale), _p(tile_expert), s)
+    if tc:
+        rows = torch.empty(cap_tiles * tile, H, dtype=x.dtype, device=dev)
+        _call("moe", "lsb_moe_gather", _p(x), _i(_dt(x)), _p(row_token), _p(row_scale), _i(on_input),
+              _i(cap_tiles * tile), _i(H), _p(rows), s)
+        _chain_ends()
+        _call("gemm_tc", "lsb_gemm_tc_grouped", _p(rows), _p(w_gate_up), _p(hidden), _i(0), _i(cap_tiles * tile),
+              _i(2 * F), _i(H), _i(E), _p(tile_expert), _i(_activation_id(activation)), s)
+        _call("gemm_tc", "lsb_gemm_tc_grouped", _p(hidden), _p(w_down), _p(y), _i(0), _i(cap_tiles * tile),
+              _i(H), _i(F), _i(E), _p(tile_expert), _i(0), s)
+    else:
+        _call("moe", "lsb_moe_up", _p(x), _i(_dt(x)), _p(row_token), _p(row_scale), _i(on_input), _p(w_gate_up),
+              _p(tile_expert), _i(cap_tiles), _p(hidden), _i(F), _i(H), _i(_activation_id(activation)), s)
+        _call("moe", "lsb_moe_down", _p(hidden), _i(_dt(x)), _p(row_token), _p(w_down), _p(tile_expert), _i(cap_tiles),
+              _p(y), _i(H), _i(F), s)
+    _call("moe", "lsb_moe_combine", _p(y), _i(1 if tc else 0), _p(pos), _p(weights), _i(1 - on_input), _i(T), _i(top),
+          _i(H), _i(cap_tiles * tile), _p(out), _i(_dt(out)), s)
 
 
 def sample(logits: torch.Tensor, params: torch.Tensor, top_k: torch.Tensor,

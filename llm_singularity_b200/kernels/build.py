@@ -43,6 +43,7 @@ SOURCES: Dict[str, object] = {          # library -> its source file (or files)
     "rownorm": "rownorm.cu",
     "linear_scan": "linear_scan.cu",
     "latent": "latent.cu",
+    "latent_tc": "latent_tc.cu",
     "moe": "moe.cu",
     "sampling": "sampling.cu",
     "random_init": "random_init.cu",

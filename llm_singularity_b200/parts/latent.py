@@ -26,7 +26,7 @@ from .base import POSITIONS, LatentPagesSpec, ParamSpec, Part, register_mixer
 @register_mixer("latent_attention")
 class LatentAttention(Part):
     graph_safe = True
-    kernels = ("gemm", "latent", "rope_cache")
+    kernels = ("gemm", "latent")
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
@@ -41,6 +41,8 @@ class LatentAttention(Part):
             if self.rot_dims > s.rot_dim:
                 raise ValueError(f"{self.rot_dims} rotating dims in a rotated part of {s.rot_dim}")
         self.width = s.kv_rank + s.rot_dim
+        if rt.dtype == torch.bfloat16:
+            self.kernels = self.kernels + ("latent_tc",)
 
     @classmethod
     def params(cls, spec) -> Dict[str, ParamSpec]:

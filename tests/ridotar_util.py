@@ -131,13 +131,29 @@ def run_cuts(runner, rid, tokens, cuts):
     return torch.cat(rows)
 
 
-def rel_err(got, want):
+def position_errors(got, want):
     """Per position: rms over the vocabulary of the difference (means taken off), over the rms of
     the wanted logits."""
     d = got.double() - want.double()
     d = d - d.mean(-1, keepdim=True)
     w = want.double() - want.double().mean(-1, keepdim=True)
-    return (d.pow(2).mean(-1).sqrt() / w.pow(2).mean().sqrt()).max().item()
+    return d.pow(2).mean(-1).sqrt() / w.pow(2).mean().sqrt()
+
+
+def rel_err(got, want):
+    return position_errors(got, want).max().item()
 
 
 TOLERANCE = {"float32": 2e-4, "bfloat16": 0.08}
+
+
+def close(got, want, dtype):
+    """32-bit: every position within the tolerance.  bfloat16: rounding can turn a router's close
+    call the other way, which changes that position (and, through a recurrent state, those after
+    it) by more than rounding; so at most one position in twenty may be outside, and the median
+    must lie far inside.  A fault of the cache, the state or the batch shows in 32-bit, where no
+    such allowance is made."""
+    e = position_errors(got, want)
+    if dtype == "float32":
+        return bool(e.max() < TOLERANCE[dtype])
+    return bool((e > TOLERANCE[dtype]).float().mean() <= 0.05 and e.median() < TOLERANCE[dtype] / 3)
