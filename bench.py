@@ -328,6 +328,25 @@ def run_ours(args):
     return 0
 
 
+def run_design(args):
+    """Prefill and decode of a design beside Llama at equal size; one JSON line of its own kind."""
+    import torch
+    from llm_singularity_b200.measure import designs
+    torch.cuda.init()
+    peaks, peak_src = load_peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    rows = designs.compare(sizes=tuple(args.sizes.split(",")), batch=args.batch, context=min(args.context, 2048),
+                           steps=min(args.steps, 32), warmup=max(args.warmup, 3),
+                           layers=args.layers if args.layers != FULL_LAYERS else None)
+    clocks = sampler.stop()
+    print(json.dumps({"metric": f"{args.design} beside llama at equal size: prefill and decode tok/s",
+                      "design": args.design, "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+                      "batch": args.batch, "context": min(args.context, 2048), "prefill_tokens": PREFILL_TOKENS,
+                      "peaks": peak_src, "clocks": clocks, "sizes": rows}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -340,6 +359,10 @@ def main():
     ap.add_argument("--windows", type=int, default=5, help="timed windows of K steps; the median is reported")
     ap.add_argument("--no-more", action="store_true", help="leave out the 3B and 8B serving runs")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--design", default=None, choices=["ridotar"],
+                    help="instead of the headline: prefill and decode throughput of this design beside the "
+                         "Llama decoder at equal size (llm_singularity_b200/measure/designs.py)")
+    ap.add_argument("--sizes", default="w1024,w2048", help="with --design: sizes to run, comma-separated")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -347,6 +370,8 @@ def main():
                           "(pip install of its source tree fails: no setup.py or pyproject.toml) "
                           "and its CMake build fetches dependencies from the network"}))
         return 0
+    if args.design:
+        return run_design(args)
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU; --gpus N > 1 is not supported")
         return 2

@@ -253,3 +253,91 @@ LSB_API int lsb_latent_attention_tc(const float* qf, const void* pages, const in
     return lsb_launch(latent_merge_kernel, dim3((unsigned)((long long)n_tokens * heads)), dim3(128), 0, stream, 1,
                       (const float*)part_o, (const float*)part_ml, (bf16*)out, splits, kv_rank);
 }
+
+// ------------------------------------------------------------------ per-head products
+// C[m, h, :] = A[m, h, :] B[h]^T for every head h on warp-level MMA: A (32-bit or bfloat16, rounded
+// to bfloat16 as an operand) with any row and head strides, B [heads, N, K] bfloat16, C 32-bit or
+// bfloat16 with any row and head strides; 32-bit accumulation.  A block makes a 64 x 64 tile of
+// one head, K in slabs of 32 staged through shared memory (so no size needs to be a multiple of
+// anything); four warps, 32 x 32 each.
+constexpr int kBtT = 64, kBtK = 32, kBtLd = kBtK + 8;
+
+template <typename TA, typename TC>
+__global__ void __launch_bounds__(128)
+batched_nt_tc_kernel(const TA* __restrict__ A, long long lda, long long a_bs, const bf16* __restrict__ B,
+                     TC* __restrict__ C, long long ldc, long long c_bs, int M, int N, int K) {
+    __shared__ __align__(32) bf16 As[kBtT * kBtLd];
+    __shared__ __align__(32) bf16 Bs[kBtT * kBtLd];
+    __shared__ __align__(32) float stage_all[4 * 256];
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int h = blockIdx.z, m0 = blockIdx.y * kBtT, n0 = blockIdx.x * kBtT;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wm = warp & 1, wn = warp >> 1;
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[2][2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) wmma::fill_fragment(acc[i][j], 0.f);
+    for (int k0 = 0; k0 < K; k0 += kBtK) {
+        for (int idx = tid; idx < kBtT * kBtK; idx += 128) {
+            const int row = idx / kBtK, col = idx % kBtK;
+            const int k = k0 + col, m = m0 + row, n = n0 + row;
+            As[row * kBtLd + col] = (m < M && k < K)
+                ? __float2bfloat16_rn(lsb_to_float(A[(size_t)m * lda + (size_t)h * a_bs + k])) : __float2bfloat16_rn(0.f);
+            Bs[row * kBtLd + col] = (n < N && k < K) ? B[((size_t)h * N + n) * K + k] : __float2bfloat16_rn(0.f);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kBtK; kk += 16) {
+            wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a[2];
+            wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                wmma::load_matrix_sync(a[i], As + (wm * 32 + i * 16) * kBtLd + kk, kBtLd);
+                wmma::load_matrix_sync(b[i], Bs + (wn * 32 + i * 16) * kBtLd + kk, kBtLd);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) wmma::mma_sync(acc[i][j], a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    float* stage = stage_all + warp * 256;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            wmma::store_matrix_sync(stage, acc[i][j], 16, wmma::mem_row_major);
+            __syncwarp();
+            const int row = lane >> 1, c0 = (lane & 1) * 8;
+            const int m = m0 + wm * 32 + i * 16 + row;
+            if (m < M) {
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    const int n = n0 + wn * 32 + j * 16 + c0 + x;
+                    if (n < N) C[(size_t)m * ldc + (size_t)h * c_bs + n] = lsb_from_float<TC>(stage[row * 16 + c0 + x]);
+                }
+            }
+            __syncwarp();
+        }
+    }
+}
+
+// ta / tc: 0 = 32-bit, 1 = bfloat16 (A and C); B is bfloat16
+LSB_API int lsb_batched_nt_tc(const void* A, int ta, long long lda, long long a_bs, const void* B, void* C, int tc,
+                              long long ldc, long long c_bs, int M, int N, int K, int batch, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
+    if (K <= 0 || batch > 65535 || (M + kBtT - 1) / kBtT > 65535) return (int)cudaErrorInvalidValue;
+    dim3 grid((N + kBtT - 1) / kBtT, (M + kBtT - 1) / kBtT, batch);
+#define LSB_BNT(TA, TC)                                                                              \
+    return lsb_launch(batched_nt_tc_kernel<TA, TC>, grid, dim3(128), 0, stream, 1, (const TA*)A, lda, a_bs, \
+                      (const bf16*)B, (TC*)C, ldc, c_bs, M, N, K)
+    if (ta == 0 && tc == 0) LSB_BNT(float, float);
+    if (ta == 0 && tc == 1) LSB_BNT(float, bf16);
+    if (ta == 1 && tc == 0) LSB_BNT(bf16, float);
+    if (ta == 1 && tc == 1) LSB_BNT(bf16, bf16);
+#undef LSB_BNT
+    return (int)cudaErrorInvalidValue;
+}

@@ -985,6 +985,10 @@ def batched_nt(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
     N = b.shape[1]
     if b.shape != (H, N, K) or out.shape != (M, H, N):
         raise KernelError(f"batched_nt: a {tuple(a.shape)}, b {tuple(b.shape)}, out {tuple(out.shape)} do not fit")
+    if LATENT_TENSOR_CORES and b.dtype == torch.bfloat16:
+        _call("latent_tc", "lsb_batched_nt_tc", _p(a), _i(_dt(a)), _ll(a.stride(0)), _ll(a.stride(1)), _p(b), _p(out),
+              _i(_dt(out)), _ll(out.stride(0)), _ll(out.stride(1)), _i(M), _i(N), _i(K), _i(H), _stream(out))
+        return
     _call("latent", "lsb_batched_nt", _p(a), _i(_dt(a)), _ll(a.stride(0)), _ll(a.stride(1)), _p(b), _i(_dt(b)),
           _p(out), _i(_dt(out)), _ll(out.stride(0)), _ll(out.stride(1)), _i(M), _i(N), _i(K), _i(H), _stream(out))
 

@@ -327,3 +327,27 @@ def test_latent_attention_kernels(tensor_cores):
                     assert (got - want).abs().max() < 0.03, (tensor_cores, q_lens, r, i)
     finally:
         K.LATENT_TENSOR_CORES = old
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tensor_cores", [False, True])
+def test_per_head_products(tensor_cores):
+    """out[m, h] = a[m, h] @ b[h].T with strided views and sizes that fill no tile."""
+    from llm_singularity_b200 import kernels as K
+    g = torch.Generator().manual_seed(8)
+    old = K.LATENT_TENSOR_CORES
+    K.LATENT_TENSOR_CORES = tensor_cores
+    try:
+        for M, H, Kd, N in ((70, 3, 20, 40), (1, 5, 128, 96), (130, 2, 72, 130)):
+            wide = torch.randn(M, H, Kd + 12, generator=g)
+            b = (torch.randn(H, N, Kd, generator=g) / 4).to(torch.bfloat16)
+            want = torch.einsum("mhk,hnk->mhn", wide[:, :, :Kd].double(), b.double())
+            for a_dtype, out_dtype in ((torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)):
+                a = wide.to(a_dtype).cuda()[:, :, :Kd]
+                out_wide = torch.zeros(M, H, N + 5, dtype=out_dtype, device="cuda")
+                K.batched_nt(a, b.cuda(), out_wide[:, :, :N])
+                got = out_wide[:, :, :N].cpu().double()
+                assert (got - want).abs().max() < 0.06 * want.abs().max(), (M, H, Kd, N, a_dtype)
+                assert float(out_wide[:, :, N:].abs().max()) == 0.0
+    finally:
+        K.LATENT_TENSOR_CORES = old
