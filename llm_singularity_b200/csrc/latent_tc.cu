@@ -30,18 +30,30 @@ constexpr int kMaxFrag = 16;            // 16-column fragments of O per warp: kv
 constexpr int kLdS = kKeys + 4;         // floats per row of the score tile
 constexpr int kLdP = kKeys + 8;         // bfloat16 per row of the weight tile
 
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
+    // 16 bytes into shared memory without passing through registers; src_bytes 0 writes zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)),
+                 "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 __global__ void __launch_bounds__(kLtThreads, 1)
 latent_attention_tc_kernel(const float* __restrict__ qf, const bf16* __restrict__ pages,
                            const int* __restrict__ q_start, const int* __restrict__ kv_len_arr,
                            const int* __restrict__ table_rows, const int* __restrict__ block_table,
                            int table_stride, bf16* __restrict__ out, float* __restrict__ part_o,
                            float* __restrict__ part_ml, int heads, int kv_rank, int rot_dim,
-                           int page_size, int num_pages, float scale, int splits) {
+                           int page_size, int num_pages, float scale, int splits, int two) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int Dk = kv_rank + rot_dim, ldk = Dk + 8;
     bf16* Qs = reinterpret_cast<bf16*>(smem);                 // [64][ldk]
-    bf16* Ks = Qs + kRows * ldk;                              // [64][ldk]
-    float* Ss = reinterpret_cast<float*>(Ks + kKeys * ldk);   // [64][kLdS]
+    bf16* Kbuf[2];                                            // [64][ldk] each; the second only if `two`
+    Kbuf[0] = Qs + kRows * ldk;
+    Kbuf[1] = Kbuf[0] + (two ? kKeys * ldk : 0);
+    float* Ss = reinterpret_cast<float*>(Kbuf[1] + kKeys * ldk);   // [64][kLdS]
     bf16* Ps = reinterpret_cast<bf16*>(Ss + kRows * kLdS);    // [64][kLdP]
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
@@ -78,22 +90,37 @@ latent_attention_tc_kernel(const float* __restrict__ qf, const bf16* __restrict_
 #pragma unroll
     for (int f = 0; f < kMaxFrag; ++f) wmma::fill_fragment(acc[f], 0.f);
 
+    // A tile of keys: four threads a cache row, every 16-byte piece an asynchronous copy of its
+    // own, all in flight at once (rows past the last key are written as zeros).  With two buffers
+    // the next tile is fetched while this one is worked on.
+    const int chunks = Dk / 8;
+    auto issue_tile = [&](int k0, bf16* dstK) {
+        const int j = tid >> 2, kj = k0 + j;
+        const bf16* src = pages;
+        int bytes = 0;
+        if (kj < kend) {
+            const int page = bt[kj / page_size];
+            if (page < 0 || page >= num_pages) lsb_set_status(LSB_BAD_PAGE);
+            else { src = pages + ((size_t)page * page_size + kj % page_size) * Dk; bytes = 16; }
+        }
+        for (int c = tid & 3; c < chunks; c += 4)
+            cp_async16(dstK + j * ldk + c * 8, bytes ? src + c * 8 : pages, bytes);
+        cp_async_commit();
+    };
+    __syncthreads();                                          // Q is in place
     for (int pass = 0; pass < 2; ++pass) {
+        int buf = 0;
+        if (kbeg < kend) issue_tile(kbeg, Kbuf[0]);
         for (int k0 = kbeg; k0 < kend; k0 += kKeys) {
-            __syncthreads();                                  // the tile before is no longer read
-            const int chunks = Dk / 8;                        // 16-byte pieces of a cache row
-            for (int i = tid; i < kKeys * chunks; i += kLtThreads) {
-                const int j = i / chunks, c = i % chunks;
-                const int kj = k0 + j;
-                uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (kj < kend) {
-                    const int page = bt[kj / page_size];
-                    if (page < 0 || page >= num_pages) lsb_set_status(LSB_BAD_PAGE);
-                    else v = *reinterpret_cast<const uint4*>(pages + ((size_t)page * page_size + kj % page_size) * Dk + c * 8);
-                }
-                *reinterpret_cast<uint4*>(Ks + j * ldk + c * 8) = v;
+            const bool more = k0 + kKeys < kend;
+            if (two && more) {
+                issue_tile(k0 + kKeys, Kbuf[buf ^ 1]);        // free since the barrier that ended the last tile
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
             }
             __syncthreads();
+            bf16* Ks = Kbuf[buf];
             {   // S = Q K^T: this warp's 16 rows x 32 keys
                 wmma::fragment<wmma::accumulator, 16, 16, 16, float> s0, s1;
                 wmma::fill_fragment(s0, 0.f);
@@ -158,6 +185,9 @@ latent_attention_tc_kernel(const float* __restrict__ qf, const bf16* __restrict_
                     }
                 }
             }
+            __syncthreads();                                  // this tile, its scores and weights are done with
+            if (two) buf ^= 1;
+            else if (more) issue_tile(k0 + kKeys, Kbuf[0]);
         }
         if (pass == 0) inv_l = l > 0.f ? 1.f / l : 0.f;
     }
@@ -217,9 +247,9 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o, const floa
     }
 }
 
-static size_t latent_tc_smem(int kv_rank, int rot_dim) {
+static size_t latent_tc_smem(int kv_rank, int rot_dim, int key_buffers = 1) {
     const size_t ldk = kv_rank + rot_dim + 8;
-    return 2 * kRows * ldk * sizeof(bf16) + kRows * kLdS * sizeof(float) + kRows * kLdP * sizeof(bf16);
+    return (1 + key_buffers) * kRows * ldk * sizeof(bf16) + kRows * kLdS * sizeof(float) + kRows * kLdP * sizeof(bf16);
 }
 
 LSB_API int lsb_latent_attention_tc_supported(int kv_rank, int rot_dim) {
@@ -239,7 +269,8 @@ LSB_API int lsb_latent_attention_tc(const float* qf, const void* pages, const in
         splits > 65535 || (splits > 1 && (!part_o || !part_ml)))
         return (int)cudaErrorInvalidValue;
     static int configured = -1;
-    const size_t smem = latent_tc_smem(kv_rank, rot_dim);
+    const int two = latent_tc_smem(kv_rank, rot_dim, 2) <= 200 * 1024 ? 1 : 0;
+    const size_t smem = latent_tc_smem(kv_rank, rot_dim, 1 + two);
     if (configured < 0)
         configured = (int)cudaFuncSetAttribute(latent_attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                200 * 1024);
@@ -248,7 +279,7 @@ LSB_API int lsb_latent_attention_tc(const float* qf, const void* pages, const in
     dim3 grid((unsigned)((rows + kRows - 1) / kRows), n_requests, splits);
     int rc = lsb_launch(latent_attention_tc_kernel, grid, dim3(kLtThreads), smem, stream, 1, qf, (const bf16*)pages,
                         q_start, kv_len, table_rows, block_table, table_stride, (bf16*)out, part_o, part_ml, heads,
-                        kv_rank, rot_dim, page_size, num_pages, scale, splits);
+                        kv_rank, rot_dim, page_size, num_pages, scale, splits, two);
     if (rc || splits == 1) return rc;
     return lsb_launch(latent_merge_kernel, dim3((unsigned)((long long)n_tokens * heads)), dim3(128), 0, stream, 1,
                       (const float*)part_o, (const float*)part_ml, (bf16*)out, splits, kv_rank);

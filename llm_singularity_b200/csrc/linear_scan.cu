@@ -15,7 +15,9 @@
 // so the result does not depend on how a prompt was cut into steps.  A column's key channels are
 // dealt to `split` neighbouring lanes (channel d = lane_part * per_thread + i), each keeping its
 // share of the column in registers; the dot with q is finished by shuffles.  The tokens' q, a, b
-// and v come through shared memory in chunks, with the activations applied on the way in.
+// and v come through shared memory in chunks of 16 tokens, with the activations applied on the way
+// in; the projections' values of the next chunk are fetched (16-byte loads where the sizes allow)
+// before the current chunk is walked, so the walk never waits for memory.
 #include "common.cuh"
 
 LSB_DEFINE_STATUS()
@@ -27,6 +29,33 @@ __device__ __forceinline__ float scan_act(float z, int act) {
     return act == 1 ? z / (1.f + expf(-z)) : z;
 }
 
+// Raw projection values of one chunk, fetched a chunk ahead so that the loads are in flight while
+// the chunk before is walked: up to kRawQ groups of eight channels of q and of k / f per thread,
+// and kRawV groups of the block's value columns.
+constexpr int kRawQ = 4, kRawV = 2;
+
+template <typename T> struct alignas(16) ScanRaw { T q[kRawQ][8]; T k[kRawQ][8]; T v[kRawV][8]; };
+
+template <typename T>
+__device__ __forceinline__ void load8(T (&dst)[8], const T* src, bool vec) {
+    if (vec) {
+        if constexpr (sizeof(T) == 2) {
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+        } else {
+            *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+            *reinterpret_cast<float4*>(dst + 4) = *reinterpret_cast<const float4*>(src + 4);
+        }
+    } else {
+#pragma unroll
+        for (int x = 0; x < 8; ++x) dst[x] = src[x];
+    }
+}
+
+// Shared-memory place of channel d of a staged token: a lane's PER channels lie together, read as
+// 16-byte vectors, and the shares of neighbouring lanes start PER + 4 words apart, which spreads
+// the lanes of a quarter warp over all banks.
+__device__ __forceinline__ int chan_slot(int d, int per, int) { return (d / per) * (per + 4) + d % per; }
+
 template <typename T, int PER>
 __global__ void __launch_bounds__(kScanThreads)
 linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_off, int v_off,
@@ -34,13 +63,14 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
                    const float* __restrict__ f_bias, const float* __restrict__ floor_,
                    int q_act, int k_act, int v_act, float* __restrict__ state, int n_slots,
                    const int* __restrict__ q_start, const int* __restrict__ table_rows,
-                   float* __restrict__ out, int split) {
+                   float* __restrict__ out, int split, int vec) {
     extern __shared__ float sh[];
     const int cols = kScanThreads / split;                  // value columns of this block
-    float* q_sh = sh;                                       // [kChunk][D]
-    float* a_sh = q_sh + kChunk * D;
-    float* b_sh = a_sh + kChunk * D;
-    float* v_sh = b_sh + kChunk * D;                        // [kChunk][cols]
+    const int Dp = (PER + 4) * split;                       // a staged token's channels, with the padding
+    float* q_sh = sh;                                       // [kChunk][Dp]
+    float* a_sh = q_sh + kChunk * Dp;
+    float* b_sh = a_sh + kChunk * Dp;
+    float* v_sh = b_sh + kChunk * Dp;                       // [kChunk][cols]
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
     const int r = blockIdx.z, h = blockIdx.y;
@@ -61,45 +91,159 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
     for (int i = 0; i < PER; ++i) S[i] = (live && d0 + i < D) ? srow[d0 + i] : 0.f;
     const float fixed = gate == 0 ? decay[h] : 0.f;
 
-    for (int base = t0; base < t1; base += kChunk) {
-        const int n = min(kChunk, t1 - base);
-        __syncthreads();
+    // groups of eight consecutive channels (or value columns) of one staged token
+    const int dg = (D + 7) / 8, vg = (cols + 7) / 8;
+    const bool fits = kChunk * dg <= kRawQ * kScanThreads && kChunk * vg <= kRawV * kScanThreads;
+    ScanRaw<T> raw;
+
+    auto fetch = [&](int base, int n) {
+#pragma unroll
+        for (int u = 0; u < kRawQ; ++u) {
+            const int g = threadIdx.x + u * kScanThreads;
+            if (g < n * dg) {
+                const int j = g / dg, d = (g % dg) * 8;
+                const T* row = proj + (size_t)(base + j) * ld + h * D + d;
+                const bool whole = vec && d + 8 <= D;
+                if (whole || d + 8 <= D) {
+                    load8(raw.q[u], row + q_off, whole);
+                    load8(raw.k[u], row + k_off, whole);
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 8; ++x) {
+                        raw.q[u][x] = d + x < D ? row[q_off + x] : lsb_from_float<T>(0.f);
+                        raw.k[u][x] = d + x < D ? row[k_off + x] : lsb_from_float<T>(0.f);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kRawV; ++u) {
+            const int g = threadIdx.x + u * kScanThreads;
+            if (g < n * vg) {
+                const int j = g / vg, c = (g % vg) * 8;
+                const T* row = proj + (size_t)(base + j) * ld + v_off + h * V + col0 + c;
+                const bool whole = vec && c + 8 <= cols && col0 + c + 8 <= V;
+                if (whole) {
+                    load8(raw.v[u], row, true);
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 8; ++x)
+                        raw.v[u][x] = (c + x < cols && col0 + c + x < V) ? row[x] : lsb_from_float<T>(0.f);
+                }
+            }
+        }
+    };
+    auto stage = [&](int n) {
+#pragma unroll
+        for (int u = 0; u < kRawQ; ++u) {
+            const int g = threadIdx.x + u * kScanThreads;
+            if (g < n * dg) {
+                const int j = g / dg, d = (g % dg) * 8;
+#pragma unroll
+                for (int x = 0; x < 8; ++x) {
+                    if (d + x >= D) break;
+                    const int at = j * Dp + chan_slot(d + x, PER, split);
+                    q_sh[at] = scan_act(lsb_to_float(raw.q[u][x]), q_act);
+                    const float z = lsb_to_float(raw.k[u][x]);
+                    if (gate == 0) {
+                        a_sh[at] = fixed;
+                        b_sh[at] = scan_act(z, k_act);
+                    } else {
+                        const float lo = floor_[h * D + d + x];
+                        const float sg = 1.f / (1.f + expf(-(z + (f_bias ? f_bias[h * D + d + x] : 0.f))));
+                        const float a = lo + (1.f - lo) * sg;
+                        a_sh[at] = a;
+                        b_sh[at] = 1.f - a;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kRawV; ++u) {
+            const int g = threadIdx.x + u * kScanThreads;
+            if (g < n * vg) {
+                const int j = g / vg, c = (g % vg) * 8;
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+                    if (c + x < cols) v_sh[j * cols + c + x] = scan_act(lsb_to_float(raw.v[u][x]), v_act);
+            }
+        }
+    };
+    // (sizes whose chunk does not fit the registers set aside above: plain loads, nothing ahead)
+    auto stage_plain = [&](int base, int n) {
         for (int i = threadIdx.x; i < n * D; i += kScanThreads) {
             const int j = i / D, d = i % D;
             const T* row = proj + (size_t)(base + j) * ld;
-            q_sh[i] = scan_act(lsb_to_float(row[q_off + h * D + d]), q_act);
+            const int at = j * Dp + chan_slot(d, PER, split);
+            q_sh[at] = scan_act(lsb_to_float(row[q_off + h * D + d]), q_act);
             const float z = lsb_to_float(row[k_off + h * D + d]);
             if (gate == 0) {
-                a_sh[i] = fixed;
-                b_sh[i] = scan_act(z, k_act);
+                a_sh[at] = fixed;
+                b_sh[at] = scan_act(z, k_act);
             } else {
                 const float lo = floor_[h * D + d];
-                const float s = 1.f / (1.f + expf(-(z + (f_bias ? f_bias[h * D + d] : 0.f))));
-                const float a = lo + (1.f - lo) * s;
-                a_sh[i] = a;
-                b_sh[i] = 1.f - a;
+                const float sg = 1.f / (1.f + expf(-(z + (f_bias ? f_bias[h * D + d] : 0.f))));
+                const float a = lo + (1.f - lo) * sg;
+                a_sh[at] = a;
+                b_sh[at] = 1.f - a;
             }
         }
         for (int i = threadIdx.x; i < n * cols; i += kScanThreads) {
             const int j = i / cols, c = col0 + i % cols;
             v_sh[i] = c < V ? scan_act(lsb_to_float(proj[(size_t)(base + j) * ld + v_off + h * V + c]), v_act) : 0.f;
         }
+    };
+
+    // channels past D (the last lane's share may reach beyond it) are staged as zeros once and
+    // never written again: a = b = q = 0 keeps their state at zero, so the walk needs no bounds
+    for (int i = threadIdx.x; i < 3 * kChunk * Dp; i += kScanThreads) sh[i] = 0.f;
+    if (fits && t0 < t1) fetch(t0, min(kChunk, t1 - t0));
+    const int mine = part * (PER + 4);
+    for (int base = t0; base < t1; base += kChunk) {
+        const int n = min(kChunk, t1 - base);
+        __syncthreads();                                    // the chunk before has been walked
+        if (fits) stage(n);
+        else stage_plain(base, n);
         __syncthreads();
-        for (int j = 0; j < n; ++j) {
-            const float v = v_sh[j * cols + lc];
-            const float* qj = q_sh + j * D + d0;
-            const float* aj = a_sh + j * D + d0;
-            const float* bj = b_sh + j * D + d0;
-            float acc = 0.f;
+        if (fits && base + kChunk < t1) fetch(base + kChunk, min(kChunk, t1 - base - kChunk));
+        // the walk: the next token's q, a and b are read (16-byte loads) while this one is worked on
+        float4 qc[PER / 4], ac[PER / 4], bc[PER / 4];
 #pragma unroll
-            for (int i = 0; i < PER; ++i) {
-                if (d0 + i < D) {
-                    S[i] = aj[i] * S[i] + bj[i] * v;
-                    acc += S[i] * qj[i];
-                }
+        for (int x = 0; x < PER / 4; ++x) {
+            qc[x] = *reinterpret_cast<const float4*>(q_sh + mine + 4 * x);
+            ac[x] = *reinterpret_cast<const float4*>(a_sh + mine + 4 * x);
+            bc[x] = *reinterpret_cast<const float4*>(b_sh + mine + 4 * x);
+        }
+        float vc = v_sh[lc];
+#pragma unroll 2
+        for (int j = 0; j < n; ++j) {
+            float4 qn[PER / 4], an[PER / 4], bn[PER / 4];
+            const int jn = j + 1 < n ? j + 1 : j;
+#pragma unroll
+            for (int x = 0; x < PER / 4; ++x) {
+                qn[x] = *reinterpret_cast<const float4*>(q_sh + jn * Dp + mine + 4 * x);
+                an[x] = *reinterpret_cast<const float4*>(a_sh + jn * Dp + mine + 4 * x);
+                bn[x] = *reinterpret_cast<const float4*>(b_sh + jn * Dp + mine + 4 * x);
             }
+            const float vn = v_sh[jn * cols + lc];
+            float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+            for (int x = 0; x < PER / 4; ++x) {
+                S[4 * x + 0] = ac[x].x * S[4 * x + 0] + bc[x].x * vc;
+                S[4 * x + 1] = ac[x].y * S[4 * x + 1] + bc[x].y * vc;
+                S[4 * x + 2] = ac[x].z * S[4 * x + 2] + bc[x].z * vc;
+                S[4 * x + 3] = ac[x].w * S[4 * x + 3] + bc[x].w * vc;
+                acc0 += S[4 * x + 0] * qc[x].x;
+                acc1 += S[4 * x + 1] * qc[x].y;
+                acc0 += S[4 * x + 2] * qc[x].z;
+                acc1 += S[4 * x + 3] * qc[x].w;
+            }
+            float acc = acc0 + acc1;
             for (int o = split >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if (part == 0 && live) out[(size_t)(base + j) * heads * V + h * V + col] = acc;
+#pragma unroll
+            for (int x = 0; x < PER / 4; ++x) { qc[x] = qn[x]; ac[x] = an[x]; bc[x] = bn[x]; }
+            vc = vn;
         }
     }
     if (live) {
@@ -134,7 +278,11 @@ LSB_API int lsb_linear_scan(const void* proj, int dtype, long long ld, int q_off
     scan_shape(D, &split, &per);
     const int cols = kScanThreads / split;
     dim3 grid((V + cols - 1) / cols, heads, n_requests);
-    const size_t smem = (size_t)kChunk * (3 * D + cols) * sizeof(float);
+    const size_t smem = (size_t)kChunk * (3 * (per + 4) * split + cols) * sizeof(float);
+    // 16-byte loads of eight channels: every group of eight must start on a 16-byte boundary
+    const int esz = dtype == LSB_F32 ? 4 : 2, al = 16 / esz;
+    const int vec = ((uintptr_t)proj % 16 == 0 && ld % al == 0 && q_off % al == 0 && k_off % al == 0 &&
+                     v_off % al == 0 && D % 8 == 0 && V % 8 == 0 && cols % 8 == 0) ? 1 : 0;
 #define LSB_SCAN_LAUNCH(PER)                                                                          \
     do {                                                                                              \
         if (smem > 48 * 1024) {                                                                       \
@@ -144,7 +292,7 @@ LSB_API int lsb_linear_scan(const void* proj, int dtype, long long ld, int q_off
         }                                                                                             \
         return lsb_launch(linear_scan_kernel<T, PER>, grid, dim3(kScanThreads), smem, stream, 1,      \
                           (const T*)proj, ld, q_off, k_off, v_off, heads, D, V, gate, decay, f_bias,  \
-                          floor_, q_act, k_act, v_act, state, n_slots, q_start, table_rows, out, split); \
+                          floor_, q_act, k_act, v_act, state, n_slots, q_start, table_rows, out, split, vec); \
     } while (0)
     LSB_DISPATCH_DTYPE(dtype, {
         if (per == 8) LSB_SCAN_LAUNCH(8);

@@ -251,19 +251,22 @@ def test_router_picks_the_largest_and_the_lower_index_of_equals():
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("weight_on", ["input", "output"])
-def test_routed_experts_kernels(dtype, weight_on):
+@pytest.mark.parametrize("sizes", [(75, 40, 28, 6, 2), (300, 64, 48, 5, 3)])
+def test_routed_experts_kernels(dtype, weight_on, sizes):
     """Tokens spread unevenly over experts (one expert gets none, one gets most), more rows than a
     tile for one of them, against a loop over tokens."""
     from llm_singularity_b200 import kernels as K
     import plain_ridotar as P
     g = torch.Generator().manual_seed(4)
-    T, H, F, E, top = 75, 40, 28, 6, 2
+    T, H, F, E, top = sizes          # the second set is one the grouped tensor-core product takes in bfloat16
     x = torch.randn(T, H, generator=g).to(dtype)
     wg, wu = (torch.randn(E, F, H, generator=g) / 6).to(dtype), (torch.randn(E, F, H, generator=g) / 6).to(dtype)
     wd = (torch.randn(E, H, F, generator=g) / 5).to(dtype)
     ids = torch.stack([torch.randperm(E - 1, generator=g)[:top] for _ in range(T)])      # expert 5 idle
-    ids[:50, 0] = 2
-    ids[:50, 1] = torch.where(ids[:50, 1] == 2, 3, ids[:50, 1])
+    most = 2 * T // 3                # two thirds of the tokens choose expert 2 first: more rows than a tile
+    ids[:most, 0] = 2
+    for k in range(1, top):
+        ids[:most, k] = torch.where(ids[:most, k] == 2, ids[:most, k].new_tensor(3 if k == 1 else 0), ids[:most, k])
     wts = torch.rand(T, top, generator=g) + 0.2
     want = torch.zeros(T, H, dtype=torch.float64)
     for t in range(T):
