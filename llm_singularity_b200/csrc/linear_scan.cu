@@ -18,6 +18,14 @@
 // and v come through shared memory in chunks of 16 tokens, with the activations applied on the way
 // in; the projections' values of the next chunk are fetched (16-byte loads where the sizes allow)
 // before the current chunk is walked, so the walk never waits for memory.
+//
+// Long portions are cut into segments that are walked side by side (MODE 1 - 3), since a walk is a
+// chain of dependent steps and one portion alone gives each SM few of them: every segment is first
+// walked from a zero state, which gives its own contribution E and the product P of its decays
+// (MODE 1, no outputs); a small kernel then chains the segments, start(s + 1) = diag(P_s) start(s)
+// + E_s, leaving each segment's start state and the request's new state; and every segment is
+// walked again from its start state for the outputs (MODE 2).  Twice the arithmetic, a chain a
+// segment long.  The sums form in another order than in one walk: equal beyond rounding.
 #include "common.cuh"
 
 LSB_DEFINE_STATUS()
@@ -25,8 +33,17 @@ LSB_DEFINE_STATUS()
 constexpr int kScanThreads = 128;
 constexpr int kChunk = 16;          // tokens staged at a time
 
+// 1 / (1 + e^-z).  Where the projections are bfloat16 their own rounding (2^-9) is five orders
+// above that of the special-function unit's exponential and reciprocal, which cost a quarter of the
+// exact ones; 32-bit storage keeps the exact functions.
+template <typename T>
+__device__ __forceinline__ float scan_sigmoid(float z) {
+    if constexpr (sizeof(T) == 2) return __fdividef(1.f, 1.f + __expf(-z));
+    else return 1.f / (1.f + expf(-z));
+}
+template <typename T>
 __device__ __forceinline__ float scan_act(float z, int act) {
-    return act == 1 ? z / (1.f + expf(-z)) : z;
+    return act == 1 ? z * scan_sigmoid<T>(z) : z;
 }
 
 // Raw projection values of one chunk, fetched a chunk ahead so that the loads are in flight while
@@ -56,14 +73,15 @@ __device__ __forceinline__ void load8(T (&dst)[8], const T* src, bool vec) {
 // the lanes of a quarter warp over all banks.
 __device__ __forceinline__ int chan_slot(int d, int per, int) { return (d / per) * (per + 4) + d % per; }
 
-template <typename T, int PER>
+template <typename T, int PER, int MODE>
 __global__ void __launch_bounds__(kScanThreads)
 linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_off, int v_off,
                    int heads, int D, int V, int gate, const float* __restrict__ decay,
                    const float* __restrict__ f_bias, const float* __restrict__ floor_,
                    int q_act, int k_act, int v_act, float* __restrict__ state, int n_slots,
                    const int* __restrict__ q_start, const int* __restrict__ table_rows,
-                   float* __restrict__ out, int split, int vec) {
+                   float* __restrict__ out, int split, int vec, int seg_len, int max_segs,
+                   float* __restrict__ seg_state, float* __restrict__ seg_decay) {
     extern __shared__ float sh[];
     const int cols = kScanThreads / split;                  // value columns of this block
     const int Dp = (PER + 4) * split;                       // a staged token's channels, with the padding
@@ -73,22 +91,35 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
     float* v_sh = b_sh + kChunk * Dp;                       // [kChunk][cols]
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
-    const int r = blockIdx.z, h = blockIdx.y;
+    const int r = MODE == 0 ? blockIdx.z : blockIdx.z / max_segs, h = blockIdx.y;
+    const int sg = MODE == 0 ? 0 : blockIdx.z % max_segs;
     const int col0 = blockIdx.x * cols;
     const int part = threadIdx.x % split, lc = threadIdx.x / split;
     const int col = col0 + lc;
-    const int t0 = q_start[r], t1 = q_start[r + 1];
+    int t0 = q_start[r], t1 = q_start[r + 1];
+    if (MODE != 0) {
+        t0 += sg * seg_len;
+        t1 = min(t1, t0 + seg_len);
+        if (t0 >= t1) return;                               // the request has fewer segments
+    }
     const int slot = table_rows[r];
     if (slot < 0 || slot >= n_slots) {
         if (threadIdx.x == 0) lsb_set_status(LSB_BAD_ROW);
         return;
     }
     const bool live = col < V;
-    float* srow = state + (((size_t)slot * heads + h) * V + (live ? col : 0)) * D;
+    // where the walk starts from and where its end goes: the request's slot, or the segment's place
+    float* srow = MODE == 0 ? state + (((size_t)slot * heads + h) * V + (live ? col : 0)) * D
+                            : seg_state + ((((size_t)r * max_segs + sg) * heads + h) * V + (live ? col : 0)) * D;
     const int d0 = part * PER;
     float S[PER];
+    float P[MODE == 1 ? PER : 1];
 #pragma unroll
-    for (int i = 0; i < PER; ++i) S[i] = (live && d0 + i < D) ? srow[d0 + i] : 0.f;
+    for (int i = 0; i < PER; ++i) S[i] = (MODE != 1 && live && d0 + i < D) ? srow[d0 + i] : 0.f;
+    if (MODE == 1) {
+#pragma unroll
+        for (int i = 0; i < (MODE == 1 ? PER : 1); ++i) P[i] = 1.f;
+    }
     const float fixed = gate == 0 ? decay[h] : 0.f;
 
     // groups of eight consecutive channels (or value columns) of one staged token
@@ -143,14 +174,14 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
                 for (int x = 0; x < 8; ++x) {
                     if (d + x >= D) break;
                     const int at = j * Dp + chan_slot(d + x, PER, split);
-                    q_sh[at] = scan_act(lsb_to_float(raw.q[u][x]), q_act);
+                    q_sh[at] = scan_act<T>(lsb_to_float(raw.q[u][x]), q_act);
                     const float z = lsb_to_float(raw.k[u][x]);
                     if (gate == 0) {
                         a_sh[at] = fixed;
-                        b_sh[at] = scan_act(z, k_act);
+                        b_sh[at] = scan_act<T>(z, k_act);
                     } else {
                         const float lo = floor_[h * D + d + x];
-                        const float sg = 1.f / (1.f + expf(-(z + (f_bias ? f_bias[h * D + d + x] : 0.f))));
+                        const float sg = scan_sigmoid<T>(z + (f_bias ? f_bias[h * D + d + x] : 0.f));
                         const float a = lo + (1.f - lo) * sg;
                         a_sh[at] = a;
                         b_sh[at] = 1.f - a;
@@ -165,7 +196,7 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
                 const int j = g / vg, c = (g % vg) * 8;
 #pragma unroll
                 for (int x = 0; x < 8; ++x)
-                    if (c + x < cols) v_sh[j * cols + c + x] = scan_act(lsb_to_float(raw.v[u][x]), v_act);
+                    if (c + x < cols) v_sh[j * cols + c + x] = scan_act<T>(lsb_to_float(raw.v[u][x]), v_act);
             }
         }
     };
@@ -175,14 +206,14 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
             const int j = i / D, d = i % D;
             const T* row = proj + (size_t)(base + j) * ld;
             const int at = j * Dp + chan_slot(d, PER, split);
-            q_sh[at] = scan_act(lsb_to_float(row[q_off + h * D + d]), q_act);
+            q_sh[at] = scan_act<T>(lsb_to_float(row[q_off + h * D + d]), q_act);
             const float z = lsb_to_float(row[k_off + h * D + d]);
             if (gate == 0) {
                 a_sh[at] = fixed;
-                b_sh[at] = scan_act(z, k_act);
+                b_sh[at] = scan_act<T>(z, k_act);
             } else {
                 const float lo = floor_[h * D + d];
-                const float sg = 1.f / (1.f + expf(-(z + (f_bias ? f_bias[h * D + d] : 0.f))));
+                const float sg = scan_sigmoid<T>(z + (f_bias ? f_bias[h * D + d] : 0.f));
                 const float a = lo + (1.f - lo) * sg;
                 a_sh[at] = a;
                 b_sh[at] = 1.f - a;
@@ -190,7 +221,7 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
         }
         for (int i = threadIdx.x; i < n * cols; i += kScanThreads) {
             const int j = i / cols, c = col0 + i % cols;
-            v_sh[i] = c < V ? scan_act(lsb_to_float(proj[(size_t)(base + j) * ld + v_off + h * V + c]), v_act) : 0.f;
+            v_sh[i] = c < V ? scan_act<T>(lsb_to_float(proj[(size_t)(base + j) * ld + v_off + h * V + c]), v_act) : 0.f;
         }
     };
 
@@ -233,23 +264,66 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
                 S[4 * x + 1] = ac[x].y * S[4 * x + 1] + bc[x].y * vc;
                 S[4 * x + 2] = ac[x].z * S[4 * x + 2] + bc[x].z * vc;
                 S[4 * x + 3] = ac[x].w * S[4 * x + 3] + bc[x].w * vc;
-                acc0 += S[4 * x + 0] * qc[x].x;
-                acc1 += S[4 * x + 1] * qc[x].y;
-                acc0 += S[4 * x + 2] * qc[x].z;
-                acc1 += S[4 * x + 3] * qc[x].w;
+                if (MODE != 1) {
+                    acc0 += S[4 * x + 0] * qc[x].x;
+                    acc1 += S[4 * x + 1] * qc[x].y;
+                    acc0 += S[4 * x + 2] * qc[x].z;
+                    acc1 += S[4 * x + 3] * qc[x].w;
+                } else {
+                    P[(MODE == 1 ? 4 * x : 0)] *= ac[x].x;
+                    P[(MODE == 1 ? 4 * x + 1 : 0)] *= ac[x].y;
+                    P[(MODE == 1 ? 4 * x + 2 : 0)] *= ac[x].z;
+                    P[(MODE == 1 ? 4 * x + 3 : 0)] *= ac[x].w;
+                }
             }
-            float acc = acc0 + acc1;
-            for (int o = split >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (part == 0 && live) out[(size_t)(base + j) * heads * V + h * V + col] = acc;
+            if (MODE != 1) {
+                float acc = acc0 + acc1;
+                for (int o = split >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (part == 0 && live) out[(size_t)(base + j) * heads * V + h * V + col] = acc;
+            }
 #pragma unroll
             for (int x = 0; x < PER / 4; ++x) { qc[x] = qn[x]; ac[x] = an[x]; bc[x] = bn[x]; }
             vc = vn;
         }
     }
+    if (MODE == 2) return;                                  // the chaining kernel has left the new state
     if (live) {
 #pragma unroll
         for (int i = 0; i < PER; ++i)
             if (d0 + i < D) srow[d0 + i] = S[i];
+    }
+    if (MODE == 1 && col0 == 0 && lc == 0) {                // the decays' product is the same for every column
+        float* prow = seg_decay + (((size_t)r * max_segs + sg) * heads + h) * D;
+#pragma unroll
+        for (int i = 0; i < (MODE == 1 ? PER : 1); ++i)
+            if (d0 + i < D) prow[d0 + i] = P[i];
+    }
+}
+
+// start(0) = the slot's state; start(s + 1) = P_s * start(s) + E_s.  seg_state holds E_s coming in
+// and start(s) going out; the slot gets the state after the last segment.
+__global__ void scan_chain_kernel(float* __restrict__ state, int n_slots, float* __restrict__ seg_state,
+                                  const float* __restrict__ seg_decay, const int* __restrict__ q_start,
+                                  const int* __restrict__ table_rows, int heads, int D, int V, int seg_len,
+                                  int max_segs) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int r = blockIdx.y;
+    const int slot = table_rows[r];
+    if (slot < 0 || slot >= n_slots) return;
+    const int n_segs = (q_start[r + 1] - q_start[r] + seg_len - 1) / seg_len;
+    const size_t per = (size_t)heads * V * D;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (size_t)gridDim.x * blockDim.x) {
+        const int d = (int)(i % D), h = (int)(i / ((size_t)V * D));
+        float cur = state[(size_t)slot * per + i];
+        for (int s = 0; s < n_segs; ++s) {
+            float* e = seg_state + ((size_t)r * max_segs + s) * per + i;
+            const float p = seg_decay[(((size_t)r * max_segs + s) * heads + h) * D + d];
+            const float contribution = *e;
+            *e = cur;
+            cur = p * cur + contribution;
+        }
+        state[(size_t)slot * per + i] = cur;
     }
 }
 
@@ -265,11 +339,15 @@ static inline void scan_shape(int D, int* split, int* per) {
 
 LSB_API int lsb_linear_scan_supported(int D) { return D > 0 && D <= 32 * 32; }
 
+// seg_len > 0 with scratch given: portions longer than a segment are walked in segments side by
+// side (see above); seg_state [requests * max_segs, heads, V, D] and seg_decay [requests * max_segs,
+// heads, D] with max_segs = ceil(max_q_len / seg_len).
 LSB_API int lsb_linear_scan(const void* proj, int dtype, long long ld, int q_off, int k_off, int v_off,
                             int heads, int D, int V, int gate, const float* decay, const float* f_bias,
                             const float* floor_, int q_act, int k_act, int v_act, float* state,
                             int n_slots, const int* q_start, const int* table_rows, int n_requests,
-                            float* out, cudaStream_t stream) {
+                            float* out, int seg_len, int max_q_len, float* seg_state, float* seg_decay,
+                            cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (heads <= 0 || V <= 0 || !lsb_linear_scan_supported(D) || heads > 65535 || n_requests > 65535)
         return (int)cudaErrorInvalidValue;
@@ -277,28 +355,48 @@ LSB_API int lsb_linear_scan(const void* proj, int dtype, long long ld, int q_off
     int split, per;
     scan_shape(D, &split, &per);
     const int cols = kScanThreads / split;
-    dim3 grid((V + cols - 1) / cols, heads, n_requests);
+    const bool segmented = seg_len > 0 && seg_state && seg_decay && max_q_len > seg_len;
+    const int max_segs = segmented ? (max_q_len + seg_len - 1) / seg_len : 1;
+    if ((long long)n_requests * max_segs > 65535) return (int)cudaErrorInvalidValue;
+    dim3 grid((V + cols - 1) / cols, heads, n_requests * max_segs);
     const size_t smem = (size_t)kChunk * (3 * (per + 4) * split + cols) * sizeof(float);
     // 16-byte loads of eight channels: every group of eight must start on a 16-byte boundary
     const int esz = dtype == LSB_F32 ? 4 : 2, al = 16 / esz;
     const int vec = ((uintptr_t)proj % 16 == 0 && ld % al == 0 && q_off % al == 0 && k_off % al == 0 &&
                      v_off % al == 0 && D % 8 == 0 && V % 8 == 0 && cols % 8 == 0) ? 1 : 0;
-#define LSB_SCAN_LAUNCH(PER)                                                                          \
+#define LSB_SCAN_LAUNCH(PER, MODE)                                                                    \
     do {                                                                                              \
         if (smem > 48 * 1024) {                                                                       \
-            int rc = (int)cudaFuncSetAttribute(linear_scan_kernel<T, PER>,                            \
+            int rc = (int)cudaFuncSetAttribute(linear_scan_kernel<T, PER, MODE>,                      \
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (rc) return rc;                                                                        \
         }                                                                                             \
-        return lsb_launch(linear_scan_kernel<T, PER>, grid, dim3(kScanThreads), smem, stream, 1,      \
+        int rc = lsb_launch(linear_scan_kernel<T, PER, MODE>, grid, dim3(kScanThreads), smem, stream, 1, \
                           (const T*)proj, ld, q_off, k_off, v_off, heads, D, V, gate, decay, f_bias,  \
-                          floor_, q_act, k_act, v_act, state, n_slots, q_start, table_rows, out, split, vec); \
+                          floor_, q_act, k_act, v_act, state, n_slots, q_start, table_rows, out, split, vec, \
+                          seg_len, max_segs, seg_state, seg_decay);                                   \
+        if (rc) return rc;                                                                            \
+    } while (0)
+#define LSB_SCAN_PER(MODE)                                                                            \
+    do {                                                                                              \
+        if (per == 8) LSB_SCAN_LAUNCH(8, MODE);                                                       \
+        else if (per == 16) LSB_SCAN_LAUNCH(16, MODE);                                                \
+        else LSB_SCAN_LAUNCH(32, MODE);                                                               \
     } while (0)
     LSB_DISPATCH_DTYPE(dtype, {
-        if (per == 8) LSB_SCAN_LAUNCH(8);
-        else if (per == 16) LSB_SCAN_LAUNCH(16);
-        else LSB_SCAN_LAUNCH(32);
+        if (!segmented) {
+            LSB_SCAN_PER(0);
+        } else {
+            LSB_SCAN_PER(1);
+            const size_t per_state = (size_t)heads * V * D;
+            const int blocks = (int)((per_state + 255) / 256 < 1024 ? (per_state + 255) / 256 : 1024);
+            int rc = lsb_launch(scan_chain_kernel, dim3(blocks, n_requests), dim3(256), 0, stream, 1, state, n_slots,
+                                seg_state, (const float*)seg_decay, q_start, table_rows, heads, D, V, seg_len, max_segs);
+            if (rc) return rc;
+            LSB_SCAN_PER(2);
+        }
     });
+#undef LSB_SCAN_PER
 #undef LSB_SCAN_LAUNCH
     return 0;
 }

@@ -885,6 +885,7 @@ def token_side_gate(g: torch.Tensor, table: torch.Tensor, token_ids: torch.Tenso
 # ------------------------------------------------------------------ linear recurrence
 SCAN_GATES = {"fixed_decay": 0, "forget": 1}
 _SCAN_ACTS = {"none": 0, "silu": 1}
+SCAN_SEGMENT = 128              # tokens of a segment when long portions are walked in segments (0: never)
 
 
 def linear_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, key_dim: int,
@@ -910,10 +911,19 @@ def linear_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: i
                 raise KernelError(f"linear_scan: {name} must have {n} entries")
     if not _lib("linear_scan").lsb_linear_scan_supported(_i(key_dim)):
         raise KernelError(f"linear_scan: key_dim {key_dim} is not supported")
+    # a few requests with long portions: segments walked side by side (twice the arithmetic, a chain
+    # a segment long); many requests, short portions and single tokens: one walk each
+    seg, seg_state, seg_decay = 0, None, None
+    if SCAN_SEGMENT and ctx.max_q_len >= 2 * SCAN_SEGMENT and ctx.n_requests <= 8:
+        seg = SCAN_SEGMENT
+        n = ctx.n_requests * -(-ctx.max_q_len // seg)
+        seg_state = torch.empty(n * heads * value_dim * key_dim, dtype=torch.float32, device=proj.device)
+        seg_decay = torch.empty(n * heads * key_dim, dtype=torch.float32, device=proj.device)
     _call("linear_scan", "lsb_linear_scan", _p(proj), _i(_dt(proj)), _ll(ld), _i(q_off), _i(k_off), _i(v_off),
           _i(heads), _i(key_dim), _i(value_dim), _i(SCAN_GATES[gate]), _p(decay), _p(f_bias), _p(floor),
           _i(_SCAN_ACTS[q_act]), _i(_SCAN_ACTS[k_act]), _i(_SCAN_ACTS[v_act]), _p(state), _i(state.shape[0]),
-          _p(ctx.q_start), _p(ctx.table_rows), _i(ctx.n_requests), _p(out), _stream(out))
+          _p(ctx.q_start), _p(ctx.table_rows), _i(ctx.n_requests), _p(out), _i(seg), _i(ctx.max_q_len),
+          _p(seg_state), _p(seg_decay), _stream(out))
 
 
 # --------------------------------------------------------------------- latent attention

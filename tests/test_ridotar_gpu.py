@@ -354,3 +354,20 @@ def test_per_head_products(tensor_cores):
                 assert float(out_wide[:, :, N:].abs().max()) == 0.0
     finally:
         K.LATENT_TENSOR_CORES = old
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["mix_a", "mix_b"])
+def test_recurrences_walked_in_segments(tmp_path, dtype, name):
+    """Portions longer than two segments are walked segment by segment, side by side, and chained:
+    with segments of 16 tokens every cutting of the portions test goes that way (portions of 150,
+    110 and 33 tokens beside shorter ones that are walked whole)."""
+    from llm_singularity_b200 import kernels as K
+    old = K.SCAN_SEGMENT
+    K.SCAN_SEGMENT = 16
+    try:
+        body_portions(tmp_path, dtype, name=name, **GPU)
+        body_mixed_batches(tmp_path, dtype, name=name, **GPU)
+    finally:
+        K.SCAN_SEGMENT = old
