@@ -36,12 +36,31 @@ __device__ __forceinline__ void group_factors(const float* row, int n, int group
     __syncthreads();
 }
 
+// four consecutive values as floats (16-byte or 8-byte accesses; the caller has checked alignment)
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
 post_group_norm_kernel(float* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ gate,
                        long long gate_stride, const float* __restrict__ gate_bias,
                        const float* __restrict__ w, T* __restrict__ copy, int n, int groups,
-                       float alpha, float eps, int keep_sum) {
+                       float alpha, float eps, int keep_sum, int vec) {
     extern __shared__ float sh[];
     float* row = sh;                 // n
     float* factor = sh + n;          // groups
@@ -49,6 +68,45 @@ post_group_norm_kernel(float* __restrict__ x, const T* __restrict__ delta, const
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
     const size_t t = blockIdx.x;
+    if (vec) {
+        // four values a thread and pass (n is a multiple of four, group borders too)
+        for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+            float s[4], d[4], z[4], b[4];
+            load4(x + t * n + i, s);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) s[k] *= alpha;
+            if (delta) {
+                load4(delta + t * n + i, d);
+                if (gate) {
+                    load4(gate + t * gate_stride + i, z);
+                    if (gate_bias) {
+                        load4(gate_bias + i, b);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) z[k] += b[k];
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) d[k] *= lsb_sigmoid(z[k]);
+                }
+#pragma unroll
+                for (int k = 0; k < 4; ++k) s[k] += d[k];
+            }
+            store4(row + i, s);
+        }
+        __syncthreads();
+        group_factors(row, n, groups, eps, factor, scratch);
+        const int gs4 = n / groups;
+        for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+            float s[4], w4[4], y[4];
+            load4(row + i, s);
+            load4(w + i, w4);
+            const float f = factor[i / gs4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) y[k] = s[k] * f * w4[k];
+            store4(x + t * n + i, keep_sum ? s : y);
+            if (copy) store4(copy + t * n + i, y);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float s = alpha * x[t * n + i];
         if (delta) {
@@ -198,9 +256,14 @@ LSB_API int lsb_post_group_norm(float* x, const void* delta, const void* gate, l
     LSB_DISPATCH_DTYPE(dtype, {
         int rc = allow_smem(post_group_norm_kernel<T>, smem);
         if (rc) return rc;
+        // vector accesses: groups of four values that never straddle a norm group, all rows aligned
+        const size_t esz = sizeof(T);
+        const int vec = (n % 4 == 0 && (n / groups) % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 &&
+                         (uintptr_t)delta % (4 * esz) == 0 && (uintptr_t)copy % (4 * esz) == 0 &&
+                         (uintptr_t)gate % (4 * esz) == 0 && gate_stride % 4 == 0 && (uintptr_t)gate_bias % 16 == 0) ? 1 : 0;
         return lsb_launch(post_group_norm_kernel<T>, dim3(rows), dim3(kRowThreads), smem, stream, 1,
                           x, (const T*)delta, (const T*)gate, gate_stride, gate_bias, w, (T*)copy, n,
-                          groups, alpha, eps, keep_sum);
+                          groups, alpha, eps, keep_sum, vec);
     });
     return 0;
 }
