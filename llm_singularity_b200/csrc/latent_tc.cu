@@ -1,4 +1,5 @@
-// Attention over a cached latent on the tensor cores (bfloat16 cache, warp-level MMA).
+// Attention over a cached latent on the tensor cores (bfloat16 cache, warp-level MMA: mma.sync
+// m16n8k16 fed by ldmatrix).
 //
 // Every head of a token reads the same cache rows (see latent.cu), so the (token, head) pairs of
 // a request are the rows of one matrix: a block takes 64 of them, Q [64, kv_rank + rot_dim], and
@@ -39,6 +40,26 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
+
+// Four 8 x 8 tiles of 16-bit values from shared memory, one row address per lane (lane i gives row
+// i % 8 of tile i / 8); register j then holds tile j in the layout the MMA wants: lane t has the
+// values (row t / 4, columns 2 (t % 4) and + 1), or with `trans` the same of the transposed tile.
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const bf16* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const bf16* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+// D (16 x 8, 32-bit) += A (16 x 16 bfloat16, rows) * B (16 x 8 bfloat16, columns)
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                 "{%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+constexpr int kMaxNt = 2 * kMaxFrag;    // 8-column tiles of O per warp
 
 __global__ void __launch_bounds__(kLtThreads, 1)
 latent_attention_tc_kernel(const float* __restrict__ qf, const bf16* __restrict__ pages,
@@ -85,10 +106,14 @@ latent_attention_tc_kernel(const float* __restrict__ qf, const bf16* __restrict_
     float m = -FLT_MAX, l = 0.f, inv_l = 0.f;
 
     const int mi = warp & 3, half = warp >> 2;
-    const int nf = kv_rank / 32;                              // fragments of O per warp
-    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc[kMaxFrag];
+    const int n_nt = kv_rank / 16;                            // 8-column tiles of O per warp (an even number)
+    float acc[kMaxNt][4];
 #pragma unroll
-    for (int f = 0; f < kMaxFrag; ++f) wmma::fill_fragment(acc[f], 0.f);
+    for (int f = 0; f < kMaxNt; ++f) { acc[f][0] = acc[f][1] = acc[f][2] = acc[f][3] = 0.f; }
+    // the rows and column offsets this lane gives to the tile loads (see ldsm_x4)
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;      // A: 16 rows x 16 k
+    const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;      // B from [n][k] rows
+    const int g = lane >> 2, tq = (lane & 3) * 2;             // this lane's row and column pair of a result tile
 
     // A tile of keys: four threads a cache row, every 16-byte piece an asynchronous copy of its
     // own, all in flight at once (rows past the last key are written as zeros).  With two buffers
@@ -121,21 +146,29 @@ latent_attention_tc_kernel(const float* __restrict__ qf, const bf16* __restrict_
             }
             __syncthreads();
             bf16* Ks = Kbuf[buf];
-            {   // S = Q K^T: this warp's 16 rows x 32 keys
-                wmma::fragment<wmma::accumulator, 16, 16, 16, float> s0, s1;
-                wmma::fill_fragment(s0, 0.f);
-                wmma::fill_fragment(s1, 0.f);
+            {   // S = Q K^T: this warp's 16 rows x 32 keys, four 16 x 8 result tiles
+                float sacc[4][4];
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) { sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f; }
+                const bf16* qa = Qs + (mi * 16 + a_row) * ldk + a_col;
+                const bf16* kb = Ks + (half * 32 + b_row) * ldk + b_col;
+#pragma unroll 4
                 for (int k = 0; k < Dk; k += 16) {
-                    wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> a;
-                    wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::col_major> b0, b1;
-                    wmma::load_matrix_sync(a, Qs + mi * 16 * ldk + k, ldk);
-                    wmma::load_matrix_sync(b0, Ks + (half * 32) * ldk + k, ldk);
-                    wmma::load_matrix_sync(b1, Ks + (half * 32 + 16) * ldk + k, ldk);
-                    wmma::mma_sync(s0, a, b0, s0);
-                    wmma::mma_sync(s1, a, b1, s1);
+                    uint32_t a[4], b01[4], b23[4];
+                    ldsm_x4(a, qa + k);
+                    ldsm_x4(b01, kb + k);                     // keys 0-15 of the warp's 32: (b0, b1) of two tiles
+                    ldsm_x4(b23, kb + 16 * ldk + k);          // keys 16-31
+                    mma_16816(sacc[0], a, b01[0], b01[1]);
+                    mma_16816(sacc[1], a, b01[2], b01[3]);
+                    mma_16816(sacc[2], a, b23[0], b23[1]);
+                    mma_16816(sacc[3], a, b23[2], b23[3]);
                 }
-                wmma::store_matrix_sync(Ss + mi * 16 * kLdS + half * 32, s0, kLdS, wmma::mem_row_major);
-                wmma::store_matrix_sync(Ss + mi * 16 * kLdS + half * 32 + 16, s1, kLdS, wmma::mem_row_major);
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    float* dst = Ss + (mi * 16 + g) * kLdS + half * 32 + nt * 8 + tq;
+                    *reinterpret_cast<float2*>(dst) = make_float2(sacc[nt][0], sacc[nt][1]);
+                    *reinterpret_cast<float2*>(dst + 8 * kLdS) = make_float2(sacc[nt][2], sacc[nt][3]);
+                }
             }
             __syncthreads();
             const float* srow_p = Ss + srow * kLdS + squarter * 16;
@@ -167,20 +200,21 @@ latent_attention_tc_kernel(const float* __restrict__ qf, const bf16* __restrict_
                     prow[c] = __float2bfloat16_rn(p);
                 }
                 __syncthreads();
-                // O += P V: this warp's 16 rows x its half of the value columns
-                wmma::fragment<wmma::matrix_a, 16, 16, 16, bf16, wmma::row_major> pa[kKeys / 16];
+                // O += P V: this warp's 16 rows x its half of the value columns.  V is the tile of keys
+                // itself, [key][dim]: its 8 x 8 pieces are transposed on the way into the registers.
+                const bf16* pa = Ps + (mi * 16 + a_row) * kLdP + a_col;
+                const bf16* vb = Ks + a_row * ldk + half * (kv_rank / 2) + a_col;
 #pragma unroll
-                for (int kk = 0; kk < kKeys / 16; ++kk)
-                    wmma::load_matrix_sync(pa[kk], Ps + mi * 16 * kLdP + kk * 16, kLdP);
+                for (int kk = 0; kk < kKeys / 16; ++kk) {
+                    uint32_t a[4];
+                    ldsm_x4(a, pa + kk * 16);
 #pragma unroll
-                for (int f = 0; f < kMaxFrag; ++f) {
-                    if (f < nf) {
-                        const int col = half * (kv_rank / 2) + f * 16;
-#pragma unroll
-                        for (int kk = 0; kk < kKeys / 16; ++kk) {
-                            wmma::fragment<wmma::matrix_b, 16, 16, 16, bf16, wmma::row_major> vb;
-                            wmma::load_matrix_sync(vb, Ks + kk * 16 * ldk + col, ldk);
-                            wmma::mma_sync(acc[f], pa[kk], vb, acc[f]);
+                    for (int f = 0; f < kMaxNt; f += 2) {
+                        if (f < n_nt) {
+                            uint32_t b[4];                    // (b0, b1) of column tile f, then of f + 1
+                            ldsm_x4_trans(b, vb + kk * 16 * ldk + f * 8);
+                            mma_16816(acc[f], a, b[0], b[1]);
+                            mma_16816(acc[f + 1], a, b[2], b[3]);
                         }
                     }
                 }
@@ -197,28 +231,23 @@ latent_attention_tc_kernel(const float* __restrict__ qf, const bf16* __restrict_
         ml[0] = m;
         ml[1] = l;
     }
-    float* stage = Ss + warp * 256;
 #pragma unroll
-    for (int f = 0; f < kMaxFrag; ++f) {
-        if (f < nf) {
-            wmma::store_matrix_sync(stage, acc[f], 16, wmma::mem_row_major);
-            __syncwarp();
-            const int row = lane >> 1, c0 = (lane & 1) * 8;
-            const int grow = row0 + mi * 16 + row;
-            const int col = half * (kv_rank / 2) + f * 16 + c0;
-            if (grow < n_rows) {
-                const float* src = stage + row * 16 + c0;
+    for (int f = 0; f < kMaxNt; ++f) {
+        if (f < n_nt) {
+            const int col = half * (kv_rank / 2) + f * 8 + tq;
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {            // rows g and g + 8 of the warp's 16
+                const int grow = row0 + mi * 16 + g + 8 * hrow;
+                if (grow >= n_rows) continue;
+                const float v0 = acc[f][2 * hrow], v1 = acc[f][2 * hrow + 1];
                 if (splits > 1) {
                     float* dst = part_o + (((size_t)qs * heads + grow) * splits + split) * kv_rank + col;
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) dst[x] = src[x];
+                    *reinterpret_cast<float2*>(dst) = make_float2(v0, v1);
                 } else {
                     bf16* dst = out + ((size_t)qs * heads + grow) * kv_rank + col;
-#pragma unroll
-                    for (int x = 0; x < 8; ++x) dst[x] = __float2bfloat16_rn(src[x]);
+                    *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(v0, v1);
                 }
             }
-            __syncwarp();
         }
     }
 }
