@@ -3,12 +3,11 @@
 //
 // Every head of a token reads the same cache rows (see latent.cu), so the (token, head) pairs of
 // a request are the rows of one matrix: a block takes 64 of them, Q [64, kv_rank + rot_dim], and
-// walks the request's keys in tiles of 64 rows of the cache.  S = Q K^T over the whole row width,
-// O += P V over the first kv_rank columns of the same tile.  The softmax is done in two passes
-// over the keys: the first finds every row's maximum and sum, the second forms the normalised
-// weights and accumulates O, so the accumulators (fragments, kept in registers) never have to be
-// rescaled row by row.  The price is a second Q K^T; what it buys is that a row's result does not
-// depend on the order in which maxima were met.
+// walks the request's keys in tiles of 64 rows of the cache.  Two warps share 16 rows: each makes
+// S = Q K^T for its half of the tile's keys over the whole row width (accumulators in registers),
+// they exchange their rows' maxima, and each writes the weights of its keys to shared memory; then
+// each adds P V for its half of the first kv_rank columns of the same tile to its part of O
+// (registers), which was rescaled by the change of the running maximum first.
 //
 // For steps of single tokens the keys of a request are split over `splits` blocks (grid.z), each
 // writing a normalised partial result with its maximum and sum; a second kernel merges them.
@@ -28,7 +27,6 @@ constexpr int kRows = 64;               // (token, head) rows per block
 constexpr int kKeys = 64;               // keys per tile
 constexpr int kLtThreads = 256;         // 8 warps: 4 row groups x 2 column halves
 constexpr int kMaxFrag = 16;            // 16-column fragments of O per warp: kv_rank <= 2 * 16 * 16
-constexpr int kLdS = kKeys + 4;         // floats per row of the score tile
 constexpr int kLdP = kKeys + 8;         // bfloat16 per row of the weight tile
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
@@ -74,8 +72,8 @@ latent_attention_tc_kernel(const float* __restrict__ qf, const bf16* __restrict_
     bf16* Kbuf[2];                                            // [64][ldk] each; the second only if `two`
     Kbuf[0] = Qs + kRows * ldk;
     Kbuf[1] = Kbuf[0] + (two ? kKeys * ldk : 0);
-    float* Ss = reinterpret_cast<float*>(Kbuf[1] + kKeys * ldk);   // [64][kLdS]
-    bf16* Ps = reinterpret_cast<bf16*>(Ss + kRows * kLdS);    // [64][kLdP]
+    bf16* Ps = Kbuf[1] + kKeys * ldk;                         // [64][kLdP]: the tile's weights
+    float* Mx = reinterpret_cast<float*>(Ps + kRows * kLdP);  // [2 halves][4 row groups][16 rows]
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
     const int r = blockIdx.y, split = blockIdx.z;
@@ -100,12 +98,15 @@ latent_attention_tc_kernel(const float* __restrict__ qf, const bf16* __restrict_
         const int row = i / Dk, d = i % Dk;
         Qs[row * ldk + d] = __float2bfloat16_rn(row0 + row < n_rows ? qsrc[(size_t)row * Dk + d] : 0.f);
     }
-    // the softmax's view: four neighbouring lanes share a row, 16 keys of the tile each
-    const int srow = tid >> 2, squarter = tid & 3;
-    const int p_row = row0 + srow < n_rows ? first_pos + (row0 + srow) / heads : -1;
-    float m = -FLT_MAX, l = 0.f, inv_l = 0.f;
-
+    // This lane's two rows of its warp's 16 (g and g + 8) and the last key each may see
     const int mi = warp & 3, half = warp >> 2;
+    const int g = lane >> 2, tq = (lane & 3) * 2;             // row and column pair of a 16 x 8 result tile
+    const int my_row[2] = {row0 + mi * 16 + g, row0 + mi * 16 + g + 8};
+    int p_row[2];
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) p_row[hr] = my_row[hr] < n_rows ? first_pos + my_row[hr] / heads : -1;
+    float m[2] = {-FLT_MAX, -FLT_MAX}, l[2] = {0.f, 0.f};     // running maximum; sum over this warp's keys
+
     const int n_nt = kv_rank / 16;                            // 8-column tiles of O per warp (an even number)
     float acc[kMaxNt][4];
 #pragma unroll
@@ -113,7 +114,6 @@ latent_attention_tc_kernel(const float* __restrict__ qf, const bf16* __restrict_
     // the rows and column offsets this lane gives to the tile loads (see ldsm_x4)
     const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;      // A: 16 rows x 16 k
     const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;      // B from [n][k] rows
-    const int g = lane >> 2, tq = (lane & 3) * 2;             // this lane's row and column pair of a result tile
 
     // A tile of keys: four threads a cache row, every 16-byte piece an asynchronous copy of its
     // own, all in flight at once (rows past the last key are written as zeros).  With two buffers
@@ -133,113 +133,152 @@ latent_attention_tc_kernel(const float* __restrict__ qf, const bf16* __restrict_
         cp_async_commit();
     };
     __syncthreads();                                          // Q is in place
-    for (int pass = 0; pass < 2; ++pass) {
-        int buf = 0;
-        if (kbeg < kend) issue_tile(kbeg, Kbuf[0]);
-        for (int k0 = kbeg; k0 < kend; k0 += kKeys) {
-            const bool more = k0 + kKeys < kend;
-            if (two && more) {
-                issue_tile(k0 + kKeys, Kbuf[buf ^ 1]);        // free since the barrier that ended the last tile
-                cp_async_wait<1>();
-            } else {
-                cp_async_wait<0>();
-            }
-            __syncthreads();
-            bf16* Ks = Kbuf[buf];
-            {   // S = Q K^T: this warp's 16 rows x 32 keys, four 16 x 8 result tiles
-                float sacc[4][4];
+    int buf = 0;
+    if (kbeg < kend) issue_tile(kbeg, Kbuf[0]);
+    for (int k0 = kbeg; k0 < kend; k0 += kKeys) {
+        const bool more = k0 + kKeys < kend;
+        if (two && more) {
+            issue_tile(k0 + kKeys, Kbuf[buf ^ 1]);            // free since the barrier that ended the last tile
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        bf16* Ks = Kbuf[buf];
+        // S = Q K^T: this warp's 16 rows x its 32 keys of the tile, four 16 x 8 result tiles
+        float sacc[4][4];
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) { sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f; }
-                const bf16* qa = Qs + (mi * 16 + a_row) * ldk + a_col;
-                const bf16* kb = Ks + (half * 32 + b_row) * ldk + b_col;
+        for (int nt = 0; nt < 4; ++nt) { sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f; }
+        {
+            const bf16* qa = Qs + (mi * 16 + a_row) * ldk + a_col;
+            const bf16* kb = Ks + (half * 32 + b_row) * ldk + b_col;
 #pragma unroll 4
-                for (int k = 0; k < Dk; k += 16) {
-                    uint32_t a[4], b01[4], b23[4];
-                    ldsm_x4(a, qa + k);
-                    ldsm_x4(b01, kb + k);                     // keys 0-15 of the warp's 32: (b0, b1) of two tiles
-                    ldsm_x4(b23, kb + 16 * ldk + k);          // keys 16-31
-                    mma_16816(sacc[0], a, b01[0], b01[1]);
-                    mma_16816(sacc[1], a, b01[2], b01[3]);
-                    mma_16816(sacc[2], a, b23[0], b23[1]);
-                    mma_16816(sacc[3], a, b23[2], b23[3]);
-                }
-#pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
-                    float* dst = Ss + (mi * 16 + g) * kLdS + half * 32 + nt * 8 + tq;
-                    *reinterpret_cast<float2*>(dst) = make_float2(sacc[nt][0], sacc[nt][1]);
-                    *reinterpret_cast<float2*>(dst + 8 * kLdS) = make_float2(sacc[nt][2], sacc[nt][3]);
-                }
+            for (int k = 0; k < Dk; k += 16) {
+                uint32_t a[4], b01[4], b23[4];
+                ldsm_x4(a, qa + k);
+                ldsm_x4(b01, kb + k);                         // keys 0-15 of the warp's 32: (b0, b1) of two tiles
+                ldsm_x4(b23, kb + 16 * ldk + k);              // keys 16-31
+                mma_16816(sacc[0], a, b01[0], b01[1]);
+                mma_16816(sacc[1], a, b01[2], b01[3]);
+                mma_16816(sacc[2], a, b23[0], b23[1]);
+                mma_16816(sacc[3], a, b23[2], b23[3]);
             }
-            __syncthreads();
-            const float* srow_p = Ss + srow * kLdS + squarter * 16;
-            if (pass == 0) {
-                float tmax = -FLT_MAX;
-                float sv[16];
+        }
+        // scale and mask; the maximum of each of the lane's rows over the warp's 32 keys
+        float hmax[2] = {-FLT_MAX, -FLT_MAX};
 #pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const int kj = k0 + squarter * 16 + c;
-                    sv[c] = (kj <= p_row && kj < kend) ? srow_p[c] * scale : -FLT_MAX;
-                    tmax = fmaxf(tmax, sv[c]);
-                }
-                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-                const float m_new = fmaxf(m, tmax);
-                float sum = 0.f;
+        for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
-                for (int c = 0; c < 16; ++c) sum += sv[c] > -FLT_MAX ? expf(sv[c] - m_new) : 0.f;
-                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                l = l * expf(m - m_new) + sum;                // m == -FLT_MAX at first: exp(-huge) = 0
-                m = m_new;
-            } else {
-                bf16* prow = Ps + srow * kLdP + squarter * 16;
+            for (int e = 0; e < 4; ++e) {
+                const int kj = k0 + half * 32 + nt * 8 + tq + (e & 1), hr = e >> 1;
+                const float v = (kj <= p_row[hr] && kj < kend) ? sacc[nt][e] * scale : -FLT_MAX;
+                sacc[nt][e] = v;
+                hmax[hr] = fmaxf(hmax[hr], v);
+            }
+        }
 #pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const int kj = k0 + squarter * 16 + c;
-                    const float p = (kj <= p_row && kj < kend) ? expf(srow_p[c] * scale - m) * inv_l : 0.f;
-                    prow[c] = __float2bfloat16_rn(p);
-                }
-                __syncthreads();
-                // O += P V: this warp's 16 rows x its half of the value columns.  V is the tile of keys
-                // itself, [key][dim]: its 8 x 8 pieces are transposed on the way into the registers.
-                const bf16* pa = Ps + (mi * 16 + a_row) * kLdP + a_col;
-                const bf16* vb = Ks + a_row * ldk + half * (kv_rank / 2) + a_col;
+        for (int hr = 0; hr < 2; ++hr) {
+            hmax[hr] = fmaxf(hmax[hr], __shfl_xor_sync(0xffffffffu, hmax[hr], 1));
+            hmax[hr] = fmaxf(hmax[hr], __shfl_xor_sync(0xffffffffu, hmax[hr], 2));
+        }
+        // the two warps that share 16 rows (one for each half of the keys) tell each other
+        if ((lane & 3) == 0) {
+            Mx[(half * 4 + mi) * 16 + g] = hmax[0];
+            Mx[(half * 4 + mi) * 16 + g + 8] = hmax[1];
+        }
+        __syncthreads();
+        float corr[2];
 #pragma unroll
-                for (int kk = 0; kk < kKeys / 16; ++kk) {
-                    uint32_t a[4];
-                    ldsm_x4(a, pa + kk * 16);
+        for (int hr = 0; hr < 2; ++hr) {
+            const float other = Mx[((half ^ 1) * 4 + mi) * 16 + g + 8 * hr];
+            const float m_new = fmaxf(m[hr], fmaxf(hmax[hr], other));
+            corr[hr] = expf(m[hr] - m_new);                   // both -FLT_MAX at first: 1, on sums that are 0
+            m[hr] = m_new;
+        }
+        // weights of the warp's 32 keys -> shared memory (bfloat16), their sums into l
+        float psum[2] = {0.f, 0.f};
 #pragma unroll
-                    for (int f = 0; f < kMaxNt; f += 2) {
-                        if (f < n_nt) {
-                            uint32_t b[4];                    // (b0, b1) of column tile f, then of f + 1
-                            ldsm_x4_trans(b, vb + kk * 16 * ldk + f * 8);
-                            mma_16816(acc[f], a, b[0], b[1]);
-                            mma_16816(acc[f + 1], a, b[2], b[3]);
-                        }
+        for (int nt = 0; nt < 4; ++nt) {
+            float p[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                p[e] = sacc[nt][e] > -FLT_MAX ? expf(sacc[nt][e] - m[e >> 1]) : 0.f;
+                psum[e >> 1] += p[e];
+            }
+            bf16* dst = Ps + (mi * 16 + g) * kLdP + half * 32 + nt * 8 + tq;
+            *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(p[0], p[1]);
+            *reinterpret_cast<__nv_bfloat162*>(dst + 8 * kLdP) = __floats2bfloat162_rn(p[2], p[3]);
+        }
+#pragma unroll
+        for (int hr = 0; hr < 2; ++hr) {
+            psum[hr] += __shfl_xor_sync(0xffffffffu, psum[hr], 1);
+            psum[hr] += __shfl_xor_sync(0xffffffffu, psum[hr], 2);
+            l[hr] = l[hr] * corr[hr] + psum[hr];
+        }
+        // what O holds was weighted against the old maximum
+#pragma unroll
+        for (int f = 0; f < kMaxNt; ++f) {
+            if (f < n_nt) {
+                acc[f][0] *= corr[0]; acc[f][1] *= corr[0];
+                acc[f][2] *= corr[1]; acc[f][3] *= corr[1];
+            }
+        }
+        __syncthreads();                                      // all 64 keys' weights are in place
+        {
+            // O += P V: this warp's 16 rows x its half of the value columns.  V is the tile of keys
+            // itself, [key][dim]: its 8 x 8 pieces are transposed on the way into the registers.
+            const bf16* pa = Ps + (mi * 16 + a_row) * kLdP + a_col;
+            const bf16* vb = Ks + a_row * ldk + half * (kv_rank / 2) + a_col;
+#pragma unroll
+            for (int kk = 0; kk < kKeys / 16; ++kk) {
+                uint32_t a[4];
+                ldsm_x4(a, pa + kk * 16);
+#pragma unroll
+                for (int f = 0; f < kMaxNt; f += 2) {
+                    if (f < n_nt) {
+                        uint32_t b[4];                        // (b0, b1) of column tile f, then of f + 1
+                        ldsm_x4_trans(b, vb + kk * 16 * ldk + f * 8);
+                        mma_16816(acc[f], a, b[0], b[1]);
+                        mma_16816(acc[f + 1], a, b[2], b[3]);
                     }
                 }
             }
-            __syncthreads();                                  // this tile, its scores and weights are done with
-            if (two) buf ^= 1;
-            else if (more) issue_tile(k0 + kKeys, Kbuf[0]);
         }
-        if (pass == 0) inv_l = l > 0.f ? 1.f / l : 0.f;
+        __syncthreads();                                      // this tile and its weights are done with
+        if (two) buf ^= 1;
+        else if (more) issue_tile(k0 + kKeys, Kbuf[0]);
     }
-    __syncthreads();                                          // Ss is free: it becomes the staging area
-    if (splits > 1 && squarter == 0 && row0 + srow < n_rows) {
-        float* ml = part_ml + (((size_t)qs * heads + row0 + srow) * splits + split) * 2;
-        ml[0] = m;
-        ml[1] = l;
+    // a row's sum is the two halves' sums (they were kept against the same maxima)
+    if ((lane & 3) == 0) {
+        Mx[(half * 4 + mi) * 16 + g] = l[0];
+        Mx[(half * 4 + mi) * 16 + g + 8] = l[1];
+    }
+    __syncthreads();
+    float inv_l[2];
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+        l[hr] += Mx[((half ^ 1) * 4 + mi) * 16 + g + 8 * hr];
+        inv_l[hr] = l[hr] > 0.f ? 1.f / l[hr] : 0.f;
+    }
+    if (splits > 1 && half == 0 && (lane & 3) == 0) {
+#pragma unroll
+        for (int hr = 0; hr < 2; ++hr) {
+            if (my_row[hr] < n_rows) {
+                float* ml = part_ml + (((size_t)qs * heads + my_row[hr]) * splits + split) * 2;
+                ml[0] = m[hr];
+                ml[1] = l[hr];
+            }
+        }
     }
 #pragma unroll
     for (int f = 0; f < kMaxNt; ++f) {
         if (f < n_nt) {
             const int col = half * (kv_rank / 2) + f * 8 + tq;
 #pragma unroll
-            for (int hrow = 0; hrow < 2; ++hrow) {            // rows g and g + 8 of the warp's 16
-                const int grow = row0 + mi * 16 + g + 8 * hrow;
+            for (int hr = 0; hr < 2; ++hr) {                  // rows g and g + 8 of the warp's 16
+                const int grow = my_row[hr];
                 if (grow >= n_rows) continue;
-                const float v0 = acc[f][2 * hrow], v1 = acc[f][2 * hrow + 1];
+                const float v0 = acc[f][2 * hr] * inv_l[hr], v1 = acc[f][2 * hr + 1] * inv_l[hr];
                 if (splits > 1) {
                     float* dst = part_o + (((size_t)qs * heads + grow) * splits + split) * kv_rank + col;
                     *reinterpret_cast<float2*>(dst) = make_float2(v0, v1);
@@ -278,7 +317,7 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o, const floa
 
 static size_t latent_tc_smem(int kv_rank, int rot_dim, int key_buffers = 1) {
     const size_t ldk = kv_rank + rot_dim + 8;
-    return (1 + key_buffers) * kRows * ldk * sizeof(bf16) + kRows * kLdS * sizeof(float) + kRows * kLdP * sizeof(bf16);
+    return (1 + key_buffers) * kRows * ldk * sizeof(bf16) + kRows * kLdP * sizeof(bf16) + 128 * sizeof(float);
 }
 
 LSB_API int lsb_latent_attention_tc_supported(int kv_rank, int rot_dim) {
@@ -325,7 +364,7 @@ constexpr int kBtT = 64, kBtK = 32, kBtLd = kBtK + 8;
 template <typename TA, typename TC>
 __global__ void __launch_bounds__(128)
 batched_nt_tc_kernel(const TA* __restrict__ A, long long lda, long long a_bs, const bf16* __restrict__ B,
-                     TC* __restrict__ C, long long ldc, long long c_bs, int M, int N, int K) {
+                     TC* __restrict__ C, long long ldc, long long c_bs, int M, int N, int K, int vec_a, int vec_b) {
     __shared__ __align__(32) bf16 As[kBtT * kBtLd];
     __shared__ __align__(32) bf16 Bs[kBtT * kBtLd];
     __shared__ __align__(32) float stage_all[4 * 256];
@@ -340,12 +379,38 @@ batched_nt_tc_kernel(const TA* __restrict__ A, long long lda, long long a_bs, co
 #pragma unroll
         for (int j = 0; j < 2; ++j) wmma::fill_fragment(acc[i][j], 0.f);
     for (int k0 = 0; k0 < K; k0 += kBtK) {
-        for (int idx = tid; idx < kBtT * kBtK; idx += 128) {
-            const int row = idx / kBtK, col = idx % kBtK;
+        // a slab of 64 rows x 32 k of each operand: 16-byte pieces where the addresses allow (the
+        // two pieces a thread fetches of each operand are independent loads), single values else
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int piece = tid + u * 128;                  // 256 pieces of 8 values
+            const int row = piece >> 2, col = (piece & 3) * 8;
             const int k = k0 + col, m = m0 + row, n = n0 + row;
-            As[row * kBtLd + col] = (m < M && k < K)
-                ? __float2bfloat16_rn(lsb_to_float(A[(size_t)m * lda + (size_t)h * a_bs + k])) : __float2bfloat16_rn(0.f);
-            Bs[row * kBtLd + col] = (n < N && k < K) ? B[((size_t)h * N + n) * K + k] : __float2bfloat16_rn(0.f);
+            bf16* da = As + row * kBtLd + col;
+            bf16* db = Bs + row * kBtLd + col;
+            if (vec_b && n < N && k + 8 <= K) {
+                *reinterpret_cast<uint4*>(db) = *reinterpret_cast<const uint4*>(B + ((size_t)h * N + n) * K + k);
+            } else {
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+                    db[x] = (n < N && k + x < K) ? B[((size_t)h * N + n) * K + k + x] : __float2bfloat16_rn(0.f);
+            }
+            const TA* pa = A + (size_t)m * lda + (size_t)h * a_bs + k;
+            if (vec_a && m < M && k + 8 <= K) {
+                if constexpr (sizeof(TA) == 2) {
+                    *reinterpret_cast<uint4*>(da) = *reinterpret_cast<const uint4*>(pa);
+                } else {
+                    const float4 lo = *reinterpret_cast<const float4*>(pa), hi = *reinterpret_cast<const float4*>(pa + 4);
+                    __nv_bfloat162 p0 = __floats2bfloat162_rn(lo.x, lo.y), p1 = __floats2bfloat162_rn(lo.z, lo.w);
+                    __nv_bfloat162 p2 = __floats2bfloat162_rn(hi.x, hi.y), p3 = __floats2bfloat162_rn(hi.z, hi.w);
+                    *reinterpret_cast<uint4*>(da) = make_uint4(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1),
+                                                               *reinterpret_cast<uint32_t*>(&p2), *reinterpret_cast<uint32_t*>(&p3));
+                }
+            } else {
+#pragma unroll
+                for (int x = 0; x < 8; ++x)
+                    da[x] = (m < M && k + x < K) ? __float2bfloat16_rn(lsb_to_float(pa[x])) : __float2bfloat16_rn(0.f);
+            }
         }
         __syncthreads();
 #pragma unroll
@@ -391,9 +456,13 @@ LSB_API int lsb_batched_nt_tc(const void* A, int ta, long long lda, long long a_
     if (M <= 0 || N <= 0 || batch <= 0) return 0;
     if (K <= 0 || batch > 65535 || (M + kBtT - 1) / kBtT > 65535) return (int)cudaErrorInvalidValue;
     dim3 grid((N + kBtT - 1) / kBtT, (M + kBtT - 1) / kBtT, batch);
+    // 16-byte loads: every piece of eight values must start on a 16-byte (A in 32-bit: 32-byte) boundary
+    const int ea = ta == 0 ? 4 : 2;
+    const int vec_a = ((uintptr_t)A % (8 * ea) == 0 && (lda * ea) % (8 * ea) == 0 && (a_bs * ea) % (8 * ea) == 0) ? 1 : 0;
+    const int vec_b = ((uintptr_t)B % 16 == 0 && K % 8 == 0) ? 1 : 0;
 #define LSB_BNT(TA, TC)                                                                              \
     return lsb_launch(batched_nt_tc_kernel<TA, TC>, grid, dim3(128), 0, stream, 1, (const TA*)A, lda, a_bs, \
-                      (const bf16*)B, (TC*)C, ldc, c_bs, M, N, K)
+                      (const bf16*)B, (TC*)C, ldc, c_bs, M, N, K, vec_a, vec_b)
     if (ta == 0 && tc == 0) LSB_BNT(float, float);
     if (ta == 0 && tc == 1) LSB_BNT(float, bf16);
     if (ta == 1 && tc == 0) LSB_BNT(bf16, float);

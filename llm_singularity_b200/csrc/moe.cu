@@ -31,13 +31,9 @@ __device__ __forceinline__ float moe_act(float z, int act) {
 
 constexpr int kMaxTop = 32;
 
-__global__ void moe_route_kernel(const float* __restrict__ logits, int n_tokens, int E, int top,
-                                 int score, int renorm, int* __restrict__ ids, float* __restrict__ wts) {
-    lsb_pdl_launch_dependents();
-    lsb_pdl_wait();
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (warp >= n_tokens) return;
-    const float* z = logits + (size_t)warp * E;
+// One warp chooses for one token (all lanes call it together).
+__device__ __forceinline__ void route_token(const float* __restrict__ z, int E, int top, int score, int renorm,
+                                            int* __restrict__ ids, float* __restrict__ wts, int lane) {
     float zmax = -FLT_MAX, denom = 1.f;
     if (score == 1) {
         for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
@@ -69,21 +65,37 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int n_tokens,
     }
     if (lane == 0) {
         for (int k = 0; k < top; ++k) {
-            ids[(size_t)warp * top + k] = chosen[k];
-            wts[(size_t)warp * top + k] = renorm ? val[k] / total : val[k];
+            ids[k] = chosen[k];
+            wts[k] = renorm ? val[k] / total : val[k];
         }
     }
 }
 
+__global__ void moe_route_kernel(const float* __restrict__ logits, int n_tokens, int E, int top,
+                                 int score, int renorm, int* __restrict__ ids, float* __restrict__ wts) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= n_tokens) return;
+    route_token(logits + (size_t)warp * E, E, top, score, renorm, ids + (size_t)warp * top, wts + (size_t)warp * top, lane);
+}
+
 __global__ void __launch_bounds__(1024)
-moe_align_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int n, int top, int E,
+moe_align_kernel(int* __restrict__ ids, float* __restrict__ wts, int n, int top, int E,
                  int cap_tiles, int tile, int* __restrict__ pos, int* __restrict__ row_token,
-                 float* __restrict__ row_scale, int* __restrict__ tile_expert) {
+                 float* __restrict__ row_scale, int* __restrict__ tile_expert,
+                 const float* __restrict__ logits, int score, int renorm) {
     extern __shared__ int shi[];
     int* counts = shi;                  // E
     int* starts = shi + E;              // E + 1, in rows
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
+    if (logits) {                       // a step of few tokens: the choosing is done here too, a warp a token
+        for (int t = threadIdx.x >> 5; t < n / top; t += blockDim.x >> 5)
+            route_token(logits + (size_t)t * E, E, top, score, renorm, ids + (size_t)t * top, wts + (size_t)t * top,
+                        threadIdx.x & 31);
+        __syncthreads();
+    }
     for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
     for (int i = threadIdx.x; i < cap_tiles * tile; i += blockDim.x) { row_token[i] = -1; row_scale[i] = 0.f; }
     for (int i = threadIdx.x; i < cap_tiles; i += blockDim.x) tile_expert[i] = -1;
@@ -175,16 +187,22 @@ moe_gemm_kernel(const T* __restrict__ A, const int* __restrict__ row_token,
     }
 }
 
+// One block per (token, choice) pair: only rows that stand for a pair are written.  The padding
+// rows of a tile keep whatever the buffer held: a row of a product depends on its own operand row
+// alone, and nothing reads the padding rows' results.
 template <typename T>
-__global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ row_token,
-                                  const float* __restrict__ row_scale, int on_input, int n, T* __restrict__ rows) {
+__global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ pos,
+                                  const float* __restrict__ wts, int on_input, int top, int capacity, int n,
+                                  T* __restrict__ rows) {
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
-    const size_t r = blockIdx.x;
-    const int tok = row_token[r];
-    const float sc = on_input ? row_scale[r] : 1.f;
+    const size_t pair = blockIdx.x;
+    const int r = pos[pair];
+    if (r < 0 || r >= capacity) return;
+    const size_t tok = pair / top;
+    const float sc = on_input ? wts[pair] : 1.f;
     for (int i = threadIdx.x; i < n; i += blockDim.x)
-        rows[r * n + i] = tok >= 0 ? lsb_from_float<T>(sc * lsb_to_float(x[(size_t)tok * n + i])) : lsb_from_float<T>(0.f);
+        rows[(size_t)r * n + i] = lsb_from_float<T>(sc * lsb_to_float(x[tok * n + i]));
 }
 
 template <typename T, typename TY>
@@ -217,23 +235,27 @@ LSB_API int lsb_moe_route(const float* logits, int n_tokens, int E, int top, int
                       dim3(32 * warps_per_block), 0, stream, 1, logits, n_tokens, E, top, score, renorm, ids, wts);
 }
 
-LSB_API int lsb_moe_align(const int* ids, const float* wts, int n_tokens, int top, int E, int cap_tiles,
+// logits given (32-bit [tokens, E]): ids and wts are chosen here first (see lsb_moe_route) and written
+LSB_API int lsb_moe_align(int* ids, float* wts, int n_tokens, int top, int E, int cap_tiles,
                           int tile, int* pos, int* row_token, float* row_scale, int* tile_expert,
-                          cudaStream_t stream) {
+                          const float* logits, int score, int renorm, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const long long n = (long long)n_tokens * top;
     if (E <= 0 || E > 8192 || tile <= 0 || cap_tiles < (n + tile - 1) / tile + E) return (int)cudaErrorInvalidValue;
+    if (logits && (top > kMaxTop || top > E || score < 0 || score > 1)) return (int)cudaErrorInvalidValue;
     return lsb_launch(moe_align_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), stream, 1,
-                      ids, wts, (int)n, top, E, cap_tiles, tile, pos, row_token, row_scale, tile_expert);
+                      ids, wts, (int)n, top, E, cap_tiles, tile, pos, row_token, row_scale, tile_expert, logits,
+                      score, renorm);
 }
 
-// rows[r] = T(scale[r] * x[row_token[r]]) (zeros in the padding): the operand of the grouped
-// tensor-core product, which wants its rows in place
-LSB_API int lsb_moe_gather(const void* x, int dtype, const int* row_token, const float* row_scale, int on_input,
-                           int capacity, int n, void* rows, cudaStream_t stream) {
-    if (capacity <= 0) return 0;
-    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(moe_gather_kernel<T>, dim3(capacity), dim3(128), 0, stream, 1,
-                                                (const T*)x, row_token, row_scale, on_input, n, (T*)rows));
+// rows[pos[t, k]] = T(wts[t, k] * x[t]): the operand of the grouped tensor-core product, which wants
+// its rows in place
+LSB_API int lsb_moe_gather(const void* x, int dtype, const int* pos, const float* wts, int on_input,
+                           int n_tokens, int top, int capacity, int n, void* rows, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(moe_gather_kernel<T>, dim3((unsigned)((long long)n_tokens * top)), dim3(128),
+                                                0, stream, 1, (const T*)x, pos, wts, on_input, top, capacity, n,
+                                                (T*)rows));
     return 0;
 }
 

@@ -1058,8 +1058,30 @@ def moe_route(logits: torch.Tensor, top: int, score: str, renormalize: bool, ids
           _i(1 if renormalize else 0), _p(ids), _p(weights), _stream(ids))
 
 
+MOE_FUSED_ROUTING_TOKENS = 256  # steps of at most this many tokens choose their experts inside the sorting kernel
+
+
+def moe_routed_experts(x: torch.Tensor, logits: torch.Tensor, top: int, score: str, renormalize: bool,
+                       w_gate_up: torch.Tensor, w_down: torch.Tensor, activation: str, weight_on: str,
+                       out: torch.Tensor) -> None:
+    """``moe_route`` on the 32-bit ``logits`` followed by ``moe_experts``; in a step of few tokens the
+    choosing rides in the kernel that sorts the rows by expert (one launch less)."""
+    _req(logits, "logits", torch.float32, 2)
+    T, E = logits.shape
+    ids = torch.empty(T, top, dtype=torch.int32, device=x.device)
+    weights = torch.empty(T, top, dtype=torch.float32, device=x.device)
+    if not 0 < top <= min(E, 32):
+        raise KernelError("moe_routed_experts: top must be in [1, min(experts, 32)]")
+    if T <= MOE_FUSED_ROUTING_TOKENS:
+        moe_experts(x, ids, weights, w_gate_up, w_down, activation, weight_on, out,
+                    route=(logits, MOE_SCORES[score], 1 if renormalize else 0))
+    else:
+        moe_route(logits, top, score, renormalize, ids, weights)
+        moe_experts(x, ids, weights, w_gate_up, w_down, activation, weight_on, out)
+
+
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
-                w_down: torch.Tensor, activation: str, weight_on: str, out: torch.Tensor) -> None:
+                w_down: torch.Tensor, activation: str, weight_on: str, out: torch.Tensor, route=None) -> None:
     """out[t] = sum over k of down_e(act(gate_e u) * up_e u), e = ids[t, k], with u = weights[t, k] * x[t]
     (``weight_on`` "input") or u = x[t] and the sum weighted ("output").  ``w_gate_up`` [E, 2F, H] has
     rows alternating gate_i, up_i; ``w_down`` [E, H, F]."""
@@ -1089,11 +1111,14 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     y = torch.empty(cap_tiles * tile, H, dtype=x.dtype if tc else torch.float32, device=dev)
     s = _stream(out)
     on_input = 1 if weight_on == "input" else 0
+    r_logits, r_score, r_renorm = route if route is not None else (None, 0, 0)
+    if r_logits is not None and r_logits.shape != (T, E):
+        raise KernelError("moe_experts: the router's logits must be [tokens, experts]")
     _call("moe", "lsb_moe_align", _p(ids), _p(weights), _i(T), _i(top), _i(E), _i(cap_tiles), _i(tile), _p(pos),
-          _p(row_token), _p(row_scale), _p(tile_expert), s)
+          _p(row_token), _p(row_scale), _p(tile_expert), _p(r_logits), _i(r_score), _i(r_renorm), s)
     if tc:
         rows = torch.empty(cap_tiles * tile, H, dtype=x.dtype, device=dev)
-        _call("moe", "lsb_moe_gather", _p(x), _i(_dt(x)), _p(row_token), _p(row_scale), _i(on_input),
+        _call("moe", "lsb_moe_gather", _p(x), _i(_dt(x)), _p(pos), _p(weights), _i(on_input), _i(T), _i(top),
               _i(cap_tiles * tile), _i(H), _p(rows), s)
         _chain_ends()
         _call("gemm_tc", "lsb_gemm_tc_grouped", _p(rows), _p(w_gate_up), _p(hidden), _i(0), _i(cap_tiles * tile),

@@ -41,8 +41,8 @@ def ridotar_config(width, layers, experts, top, ff, kv_rank, vocab) -> dict:
             out.append({"type": "latent_attention", "mlp": mlp, "mixer": dict(latent)})
         else:
             out.append({"type": "latent_attention", "mlp": mlp, "mixer": dict(latent, kv_from=i - 1)})
-    return {"architecture": "Ridotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5, "groups": 2},
-            "postln_alpha": 2.0, "token_side": {"dim": 32}, "layers": out}
+    return {"architecture": "Ridotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 4},
+            "postln_alpha": 1.5, "token_side": {"dim": 32}, "layers": out}
 
 
 def llama_config(width, layers, experts, top, ff, kv_rank, vocab) -> dict:

@@ -60,9 +60,7 @@ class RoutedExperts(Part):
     def forward(self, x, ctx):
         s, ops, T = self.spec, self.rt.ops, x.shape[0]
         logits = ops.linear(x, self.w_router, out_dtype=torch.float32)
-        ids = self.rt.empty(T, s.top, dtype=torch.int32)
-        weights = self.rt.empty(T, s.top, dtype=torch.float32)
-        ops.moe_route(logits, s.top, s.score, s.renormalize, ids, weights)
         out = self.rt.empty(T, s.hidden_size)
-        ops.moe_experts(x, ids, weights, self.w_gate_up, self.w_down, s.activation, s.weight_on, out)
+        ops.moe_routed_experts(x, logits, s.top, s.score, s.renormalize, self.w_gate_up, self.w_down,
+                               s.activation, s.weight_on, out)
         return out

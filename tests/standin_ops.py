@@ -304,3 +304,10 @@ def moe_experts(x, ids, weights, w_gate_up, w_down, activation, weight_on, out):
             y = w_down[e].float() @ a
             acc[t] += y if weight_on == "input" else w * y
     out.copy_(acc.to(out.dtype))
+
+
+def moe_routed_experts(x, logits, top, score, renormalize, w_gate_up, w_down, activation, weight_on, out):
+    ids = torch.empty(logits.shape[0], top, dtype=torch.int32)
+    weights = torch.empty(logits.shape[0], top, dtype=torch.float32)
+    moe_route(logits, top, score, renormalize, ids, weights)
+    moe_experts(x, ids, weights, w_gate_up, w_down, activation, weight_on, out)
