@@ -201,8 +201,23 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict
     if (r < 0 || r >= capacity) return;
     const size_t tok = pair / top;
     const float sc = on_input ? wts[pair] : 1.f;
+    const T* src = x + tok * n;
+    T* dst = rows + (size_t)r * n;
+    if (sizeof(T) == 2 && n % 8 == 0 && (((uintptr_t)x | (uintptr_t)rows) & 15) == 0) {
+        for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {      // 16 bytes a thread and pass
+            uint4 raw = *reinterpret_cast<const uint4*>(src + i);
+            __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __bfloat1622float2(p[k]);
+                p[k] = __floats2bfloat162_rn(sc * f.x, sc * f.y);
+            }
+            *reinterpret_cast<uint4*>(dst + i) = raw;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < n; i += blockDim.x)
-        rows[(size_t)r * n + i] = lsb_from_float<T>(sc * lsb_to_float(x[tok * n + i]));
+        dst[i] = lsb_from_float<T>(sc * lsb_to_float(src[i]));
 }
 
 template <typename T, typename TY>
