@@ -51,6 +51,16 @@ CONFIGS = {
             _layer("hgrn2", {"heads": 1, "dim": 80, "vdim": 48}, _moe(4, 4, 32)),
             _layer("latent_attention", _lat(4, 32, 32, 16, 48, 64, 16, 10000.0), None),
         ]},
+    # nothing a multiple of eight: the products, the cache rows and the scans take their plain paths
+    "mix_c": {
+        "architecture": "Ridotar", "vocab": 53, "width": 100, "norm": {"eps": 1e-5, "groups": 5},
+        "postln_alpha": 0.75, "token_side": {"dim": 7},
+        "layers": [
+            _layer("hgrn2", {"heads": 3, "dim": 10, "vdim": 14}, _moe(3, 3, 30)),
+            _layer("latent_attention", _lat(5, 6, 10, 6, 22, 18, 4, 700.0), _moe(3, 2, 30)),
+            _layer("lightning", {"heads": 1, "dim": 26, "vdim": 22, "decay": [0.97]}, None),
+            _layer("latent_attention", _lat(2, 14, 6, 6, 10, 18, 4, 700.0, kv_from=1), _moe(4, 1, 18)),
+        ]},
 }
 
 

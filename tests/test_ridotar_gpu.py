@@ -155,14 +155,14 @@ def test_each_mixer_alone(tmp_path, dtype):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mix_a", "mix_b"])
+@pytest.mark.parametrize("name", ["mix_a", "mix_b", "mix_c"])
 def test_portions_of_any_size(tmp_path, dtype, name):
     body_portions(tmp_path, dtype, name=name, **GPU)
 
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mix_a", "mix_b"])
+@pytest.mark.parametrize("name", ["mix_a", "mix_b", "mix_c"])
 def test_mixed_batches_with_slots_and_pages_used_again(tmp_path, dtype, name):
     body_mixed_batches(tmp_path, dtype, name=name, **GPU)
 

@@ -24,6 +24,7 @@ def test_portions_on_the_host(tmp_path):
 def test_mixed_batches_on_the_host(tmp_path):
     G.body_mixed_batches(tmp_path, "float32", name="mix_a", **HOST)
     G.body_mixed_batches(tmp_path, "float32", name="mix_b", **HOST)
+    G.body_mixed_batches(tmp_path, "float32", name="mix_c", **HOST)
 
 
 def test_greedy_generation_on_the_host(tmp_path):
