@@ -136,12 +136,12 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
                 const T* row = proj + (size_t)(base + j) * ld + h * D + d;
                 const bool whole = vec && d + 8 <= D;
                 if (whole || d + 8 <= D) {
-                    load8(raw.q[u], row + q_off, whole);
+                    if (MODE != 1) load8(raw.q[u], row + q_off, whole);      // (a segment's first walk makes no outputs)
                     load8(raw.k[u], row + k_off, whole);
                 } else {
 #pragma unroll
                     for (int x = 0; x < 8; ++x) {
-                        raw.q[u][x] = d + x < D ? row[q_off + x] : lsb_from_float<T>(0.f);
+                        if (MODE != 1) raw.q[u][x] = d + x < D ? row[q_off + x] : lsb_from_float<T>(0.f);
                         raw.k[u][x] = d + x < D ? row[k_off + x] : lsb_from_float<T>(0.f);
                     }
                 }
@@ -174,7 +174,7 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
                 for (int x = 0; x < 8; ++x) {
                     if (d + x >= D) break;
                     const int at = j * Dp + chan_slot(d + x, PER, split);
-                    q_sh[at] = scan_act<T>(lsb_to_float(raw.q[u][x]), q_act);
+                    if (MODE != 1) q_sh[at] = scan_act<T>(lsb_to_float(raw.q[u][x]), q_act);
                     const float z = lsb_to_float(raw.k[u][x]);
                     if (gate == 0) {
                         a_sh[at] = fixed;
@@ -206,7 +206,7 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
             const int j = i / D, d = i % D;
             const T* row = proj + (size_t)(base + j) * ld;
             const int at = j * Dp + chan_slot(d, PER, split);
-            q_sh[at] = scan_act<T>(lsb_to_float(row[q_off + h * D + d]), q_act);
+            if (MODE != 1) q_sh[at] = scan_act<T>(lsb_to_float(row[q_off + h * D + d]), q_act);
             const float z = lsb_to_float(row[k_off + h * D + d]);
             if (gate == 0) {
                 a_sh[at] = fixed;
@@ -316,12 +316,21 @@ __global__ void scan_chain_kernel(float* __restrict__ state, int n_slots, float*
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (size_t)gridDim.x * blockDim.x) {
         const int d = (int)(i % D), h = (int)(i / ((size_t)V * D));
         float cur = state[(size_t)slot * per + i];
-        for (int s = 0; s < n_segs; ++s) {
-            float* e = seg_state + ((size_t)r * max_segs + s) * per + i;
-            const float p = seg_decay[(((size_t)r * max_segs + s) * heads + h) * D + d];
-            const float contribution = *e;
-            *e = cur;
-            cur = p * cur + contribution;
+        for (int s0 = 0; s0 < n_segs; s0 += 8) {             // eight segments' loads in flight at once
+            float e[8], p[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int s = s0 + k < n_segs ? s0 + k : n_segs - 1;
+                e[k] = seg_state[((size_t)r * max_segs + s) * per + i];
+                p[k] = seg_decay[(((size_t)r * max_segs + s) * heads + h) * D + d];
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (s0 + k < n_segs) {
+                    seg_state[((size_t)r * max_segs + s0 + k) * per + i] = cur;
+                    cur = p[k] * cur + e[k];
+                }
+            }
         }
         state[(size_t)slot * per + i] = cur;
     }
