@@ -27,8 +27,12 @@ class PartSpec:
 # --------------------------------------------------------------------------- norms
 @dataclass(frozen=True)
 class RMSNormSpec(PartSpec):
+    """``x / sqrt(mean(x^2) + eps) * w``.  ``unit_offset``: the stored weight is the distance from
+    one, ``w = 1 + stored``."""
+
     size: int = 0
     eps: float = 1e-5
+    unit_offset: bool = False
     kind: str = field(init=False, default="rmsnorm")
 
 
@@ -116,6 +120,72 @@ class LinearRecurrenceSpec(PartSpec):
     out_gate: bool = False
     eps: float = 1e-5
     kind: str = field(init=False, default="linear_recurrence")
+
+
+@dataclass(frozen=True)
+class KVAttentionSpec(PartSpec):
+    """Softmax attention with grouped keys/values over a paged cache whose keys (``key_dim``, shared
+    with the queries) and values (``value_dim``) have sizes of their own.  What may stand between the
+    projections and the scores, each optional: biases on q, k and v (``qkv_bias``); an RMS norm per
+    head of q and of k with one weight of head size each (``qk_norm``, ``eps``), before the rotation;
+    a query temperature, ``q *= 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)`` (``temp_every``
+    0: none); a rotation (``position``).  A query sees the keys not after it that lie within
+    ``window`` positions (None: all) and in its own chunk of ``chunk`` positions counted from the
+    start of the sequence (None: no chunks).  ``out_gate``: the heads' outputs are multiplied by
+    sigmoid(W_g x) before the output projection."""
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    scale: float = 0.0
+    window: Optional[int] = None
+    chunk: Optional[int] = None
+    qkv_bias: bool = False
+    qk_norm: bool = False
+    eps: float = 1e-5
+    temp_coef: float = 0.0
+    temp_every: int = 0
+    out_gate: bool = False
+    position: PartSpec = field(default_factory=NoPositionSpec)
+    kind: str = field(init=False, default="kv_attention")
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec(PartSpec):
+    """A matrix memory per head with an exponential input gate (the mLSTM cell).  With q scaled by
+    ``key_dim^-1/2``, log gates ``i = cap tanh((W_i x + b_i) / cap)`` and ``f = logsigmoid(cap
+    tanh((W_f x + b_f) / cap))`` per head, and a running maximum m that starts at 0:
+
+        m_t = max(f + m_(t-1), i)
+        S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T        n_t likewise with k alone
+        o_t = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6)
+
+    Each head's o is brought to unit rms (``eps``), the heads are concatenated and multiplied by one
+    weight over all of them and by sigmoid(W_g x) (``out_gate``), then projected by W_o."""
+
+    hidden_size: int = 0
+    num_heads: int = 0
+    key_dim: int = 0
+    value_dim: int = 0
+    gate_cap: float = 15.0
+    out_gate: bool = True
+    eps: float = 1e-5
+    kind: str = field(init=False, default="matrix_memory")
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec(PartSpec):
+    """Mixers side by side on one input: each branch's result is RMS-normed over the model width
+    with a weight of its own (``eps``), and the mean of those is the mixer's result.  ``names`` are
+    the branches' names in parameter paths."""
+
+    hidden_size: int = 0
+    branches: Tuple[PartSpec, ...] = ()
+    names: Tuple[str, ...] = ()
+    eps: float = 1e-5
+    kind: str = field(init=False, default="parallel")
 
 
 @dataclass(frozen=True)
@@ -216,6 +286,21 @@ class PostNormBlockSpec(PartSpec):
 
 
 @dataclass(frozen=True)
+class SandwichBlockSpec(PartSpec):
+    """x += mult * post1(mixer(norm1(x))); x += mult * post2(ffn(norm2(x)))   (the "sandwich_norm"
+    arrangement: a norm in front of and behind every sublayer).  ``ffn`` None: no second step."""
+
+    mixer: PartSpec = None
+    ffn: Optional[PartSpec] = None
+    mixer_norm: PartSpec = None
+    mixer_post_norm: PartSpec = None
+    ffn_norm: Optional[PartSpec] = None
+    ffn_post_norm: Optional[PartSpec] = None
+    residual_mult: float = 1.0
+    kind: str = field(init=False, default="sandwich_norm")
+
+
+@dataclass(frozen=True)
 class LayerCall:
     """One entry of the run order.
 
@@ -229,6 +314,9 @@ class LayerCall:
     block: int
     cache: int
     writes_cache: bool = True
+    # row of the model's step vectors (``ModelSpec.step_vectors`` rows of model width) that is added
+    # to the stream right before this call: the number of the pass a looped stretch begins here
+    step: Optional[int] = None
 
 
 # ---------------------------------------------------------------------------- model
@@ -237,6 +325,7 @@ class EmbeddingSpec(PartSpec):
     vocab_size: int = 0
     hidden_size: int = 0
     side_size: int = 0            # columns of a second table of per-token inputs for the blocks (0: none)
+    scale: float = 1.0            # multiplies the looked-up row on its way into the stream
     kind: str = field(init=False, default="embedding")
 
 
@@ -260,12 +349,13 @@ class ModelSpec:
     head: HeadSpec
     # checkpoint tensor name -> (owner path, local parameter name); owner paths are
     # "embedding", "head", "head.norm", "blocks.<i>.mixer", "blocks.<i>.ffn",
-    # "blocks.<i>.mixer_norm", "blocks.<i>.ffn_norm".
+    # "blocks.<i>.mixer_norm", "blocks.<i>.ffn_norm", "steps".
     tensor_names: Tuple[Tuple[str, Tuple[str, str]], ...]
     # names that may be present in a checkpoint and are skipped without complaint
     ignorable: Tuple[str, ...] = ()
     stop_token_ids: Tuple[int, ...] = ()
     max_position_embeddings: int = 0
+    step_vectors: int = 0         # rows of the table of vectors that run-order entries add to the stream
 
     @property
     def num_caches(self) -> int:

@@ -1,0 +1,145 @@
+// What happens to queries, keys and values between their projection and the attention itself,
+// for mixers whose key size and value size may differ, as one kernel per step:
+//
+//   * a bias per channel (q, k, v), added in 32-bit;
+//   * a norm per head of q and of k: z / sqrt(mean(z^2) + eps) * w, one weight of head size for
+//     all heads of q and one for all heads of k;
+//   * a query temperature: q *= 1 + coef * ln(floor((pos + 1) / every) + 1);
+//   * rotation of the first `rotary_dim` dims of every q and k head by pos * inv_freq[i], pairs
+//     (2i, 2i + 1) ("adjacent") or (i, i + rotary_dim / 2) ("half"), angle formed in 32-bit;
+//   * queries go to q_out [tokens, nh * dk]; keys and values to the token's place in the cache
+//     pages, [page][kv head][offset][dk] and [page][kv head][offset][dv].
+//
+// Each of the first four is optional.  The projections come as rows of one matrix, q at q_off, k
+// at k_off, v at v_off, in the compute dtype.  One block per token, one warp per head at a time;
+// a head waits in shared memory between the norm and the rotation.
+#include "common.cuh"
+
+LSB_DEFINE_STATUS()
+
+constexpr int kPrepWarps = 4;
+constexpr int kPrepMaxDim = 512;
+
+struct PrepArgs {
+    const void* proj; long long ld; int q_off, k_off, v_off;
+    int nh, nkv, dk, dv;
+    const float *q_bias, *k_bias, *v_bias;
+    const float *q_norm, *k_norm; float norm_eps;
+    float temp_coef; int temp_every;
+    const float* inv_freq; int rotary_dim, adjacent;
+    const int *positions, *token_req, *table_rows, *block_table; int table_stride;
+    void *q_out, *k_pages, *v_pages; int page_size, num_pages, store;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArgs a) {
+    __shared__ float head_sh[kPrepWarps][kPrepMaxDim];
+    lsb_pdl_launch_dependents();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pos = a.positions[t];
+    float temp = 1.f;
+    if (a.temp_every > 0) temp = 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every) + 1.f);
+    lsb_pdl_wait();                                 // (the block table is written by a kernel of this step)
+    long long k_base = -1, v_base = -1;             // element offsets of (page, head 0, offset, 0)
+    if (a.store) {
+        const int r = a.token_req[t];
+        const int page_idx = pos / a.page_size;
+        int page = -1;
+        if (page_idx < a.table_stride) page = a.block_table[(size_t)a.table_rows[r] * a.table_stride + page_idx];
+        if (page < 0 || page >= a.num_pages) {
+            if (threadIdx.x == 0) lsb_set_status(LSB_BAD_PAGE);
+        } else {
+            const long long at = (long long)page * a.nkv * a.page_size + (pos % a.page_size);
+            k_base = at * a.dk;
+            v_base = at * a.dv;
+        }
+    }
+    const T* row = (const T*)a.proj + (size_t)t * a.ld;
+    const int half_rot = a.rotary_dim >> 1;
+    float* hs = head_sh[warp];
+    for (int head = warp; head < a.nh + a.nkv; head += kPrepWarps) {
+        const bool is_q = head < a.nh;
+        const int hh = is_q ? head : head - a.nh;
+        const T* src = row + (is_q ? a.q_off : a.k_off) + (size_t)hh * a.dk;
+        const float* bias = is_q ? a.q_bias : a.k_bias;
+        const float* nw = is_q ? a.q_norm : a.k_norm;
+        float ss = 0.f;
+        for (int d = lane; d < a.dk; d += 32) {
+            float x = lsb_to_float(src[d]);
+            if (bias) x += bias[hh * a.dk + d];
+            hs[d] = x;
+            ss += x * x;
+        }
+        float inv = 1.f;
+        if (nw) inv = rsqrtf(lsb_warp_sum(ss) / (float)a.dk + a.norm_eps);
+        const float mul = is_q ? temp : 1.f;
+        __syncwarp();
+        T* dst = nullptr;
+        if (is_q) dst = (T*)a.q_out + ((size_t)t * a.nh + hh) * a.dk;
+        else if (k_base >= 0) dst = (T*)a.k_pages + k_base + (long long)hh * a.page_size * a.dk;
+        if (dst) {
+            // work items: pairs of dims; the rotating pairs first, then the rest two by two
+            const int pairs = (a.dk + 1) >> 1;
+            for (int i = lane; i < pairs; i += 32) {
+                int ia, ib;
+                if (i < half_rot) {
+                    ia = a.adjacent ? 2 * i : i;
+                    ib = a.adjacent ? 2 * i + 1 : i + half_rot;
+                } else {
+                    ia = a.rotary_dim + 2 * (i - half_rot);
+                    ib = ia + 1;
+                }
+                float x0 = hs[ia] * (nw ? inv * nw[ia] : 1.f) * mul;
+                float x1 = ib < a.dk ? hs[ib] * (nw ? inv * nw[ib] : 1.f) * mul : 0.f;
+                if (i < half_rot) {
+                    float s, c;
+                    sincosf((float)pos * a.inv_freq[i], &s, &c);
+                    const float r0 = x0 * c - x1 * s, r1 = x1 * c + x0 * s;
+                    x0 = r0;
+                    x1 = r1;
+                }
+                dst[ia] = lsb_from_float<T>(x0);
+                if (ib < a.dk) dst[ib] = lsb_from_float<T>(x1);
+            }
+        }
+        __syncwarp();
+    }
+    if (v_base >= 0) {
+        const T* v = row + a.v_off;
+        for (int w = threadIdx.x; w < a.nkv * a.dv; w += blockDim.x) {
+            const int head = w / a.dv, d = w - head * a.dv;
+            float x = lsb_to_float(v[w]);
+            if (a.v_bias) x += a.v_bias[w];
+            ((T*)a.v_pages)[v_base + (long long)head * a.page_size * a.dv + d] = lsb_from_float<T>(x);
+        }
+    }
+}
+
+LSB_API int lsb_attention_prep_max_dim() { return kPrepMaxDim; }
+
+LSB_API int lsb_attention_prep(const void* proj, int dtype, long long ld, int q_off, int k_off, int v_off, int tokens,
+                               int nh, int nkv, int dk, int dv, const float* q_bias, const float* k_bias,
+                               const float* v_bias, const float* q_norm, const float* k_norm, float norm_eps,
+                               float temp_coef, int temp_every, const float* inv_freq, int rotary_dim, int adjacent,
+                               const int* positions, const int* token_req, const int* table_rows,
+                               const int* block_table, int table_stride, void* q_out, void* k_pages, void* v_pages,
+                               int page_size, int num_pages, int store, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (dk <= 0 || dk > kPrepMaxDim || dv <= 0 || nh <= 0 || nkv <= 0 || rotary_dim % 2 || rotary_dim > dk ||
+        rotary_dim < 0 || (rotary_dim > 0 && !inv_freq))
+        return (int)cudaErrorInvalidValue;
+    PrepArgs a;
+    a.proj = proj; a.ld = ld; a.q_off = q_off; a.k_off = k_off; a.v_off = v_off;
+    a.nh = nh; a.nkv = nkv; a.dk = dk; a.dv = dv;
+    a.q_bias = q_bias; a.k_bias = k_bias; a.v_bias = v_bias;
+    a.q_norm = q_norm; a.k_norm = k_norm; a.norm_eps = norm_eps;
+    a.temp_coef = temp_coef; a.temp_every = temp_every;
+    a.inv_freq = inv_freq; a.rotary_dim = rotary_dim; a.adjacent = adjacent;
+    a.positions = positions; a.token_req = token_req; a.table_rows = table_rows; a.block_table = block_table;
+    a.table_stride = table_stride;
+    a.q_out = q_out; a.k_pages = k_pages; a.v_pages = v_pages; a.page_size = page_size; a.num_pages = num_pages;
+    a.store = store;
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(attention_prep_kernel<T>, dim3(tokens), dim3(kPrepWarps * 32), 0, stream,
+                                                1, a));
+    return 0;
+}

@@ -9,7 +9,12 @@
 //
 //   gate 0 (fixed decay):  a = decay[head] for every channel,  b = act_k(k projection)
 //   gate 1 (forget gate):  a = floor + (1 - floor) * sigmoid(f projection + bias),  b = 1 - a
-//   q = act_q(q projection), v = act_v(v projection); act: 0 none, 1 silu
+//   gate 2 (given):        a = keep[token, head] and b = write[token, head] * act_k(k projection), two
+//                          numbers per token and head that another kernel has made (a memory
+//                          whose gates are scalars per head); with `ones` a value column of ones
+//                          rides along behind the V columns of the projection, so that the state
+//                          has V + 1 columns and the last column of the output is (sum of b) . q
+//   q = act_q(q projection) * q_scale, v = act_v(v projection); act: 0 none, 1 silu
 //
 // A block owns (request, head, a tile of value columns) and walks the request's tokens in order,
 // so the result does not depend on how a prompt was cut into steps.  A column's key channels are
@@ -81,7 +86,8 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
                    int q_act, int k_act, int v_act, float* __restrict__ state, int n_slots,
                    const int* __restrict__ q_start, const int* __restrict__ table_rows,
                    float* __restrict__ out, int split, int vec, int seg_len, int max_segs,
-                   float* __restrict__ seg_state, float* __restrict__ seg_decay) {
+                   float* __restrict__ seg_state, float* __restrict__ seg_decay,
+                   const float* __restrict__ g_keep, const float* __restrict__ g_write, int ones, float q_scale) {
     extern __shared__ float sh[];
     const int cols = kScanThreads / split;                  // value columns of this block
     const int Dp = (PER + 4) * split;                       // a staged token's channels, with the padding
@@ -107,10 +113,11 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
         if (threadIdx.x == 0) lsb_set_status(LSB_BAD_ROW);
         return;
     }
-    const bool live = col < V;
+    const int Vs = V + ones;                                // columns of the state and of the output
+    const bool live = col < Vs;
     // where the walk starts from and where its end goes: the request's slot, or the segment's place
-    float* srow = MODE == 0 ? state + (((size_t)slot * heads + h) * V + (live ? col : 0)) * D
-                            : seg_state + ((((size_t)r * max_segs + sg) * heads + h) * V + (live ? col : 0)) * D;
+    float* srow = MODE == 0 ? state + (((size_t)slot * heads + h) * Vs + (live ? col : 0)) * D
+                            : seg_state + ((((size_t)r * max_segs + sg) * heads + h) * Vs + (live ? col : 0)) * D;
     const int d0 = part * PER;
     float S[PER];
     float P[MODE == 1 ? PER : 1];
@@ -160,11 +167,12 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
 #pragma unroll
                     for (int x = 0; x < 8; ++x)
                         raw.v[u][x] = (c + x < cols && col0 + c + x < V) ? row[x] : lsb_from_float<T>(0.f);
+                    // (the column of ones is put in when the chunk is staged)
                 }
             }
         }
     };
-    auto stage = [&](int n) {
+    auto stage = [&](int base, int n) {
 #pragma unroll
         for (int u = 0; u < kRawQ; ++u) {
             const int g = threadIdx.x + u * kScanThreads;
@@ -174,11 +182,14 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
                 for (int x = 0; x < 8; ++x) {
                     if (d + x >= D) break;
                     const int at = j * Dp + chan_slot(d + x, PER, split);
-                    if (MODE != 1) q_sh[at] = scan_act<T>(lsb_to_float(raw.q[u][x]), q_act);
+                    if (MODE != 1) q_sh[at] = scan_act<T>(lsb_to_float(raw.q[u][x]), q_act) * q_scale;
                     const float z = lsb_to_float(raw.k[u][x]);
                     if (gate == 0) {
                         a_sh[at] = fixed;
                         b_sh[at] = scan_act<T>(z, k_act);
+                    } else if (gate == 2) {
+                        a_sh[at] = g_keep[(size_t)(base + j) * heads + h];
+                        b_sh[at] = g_write[(size_t)(base + j) * heads + h] * scan_act<T>(z, k_act);
                     } else {
                         const float lo = floor_[h * D + d + x];
                         const float sg = scan_sigmoid<T>(z + (f_bias ? f_bias[h * D + d + x] : 0.f));
@@ -196,7 +207,9 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
                 const int j = g / vg, c = (g % vg) * 8;
 #pragma unroll
                 for (int x = 0; x < 8; ++x)
-                    if (c + x < cols) v_sh[j * cols + c + x] = scan_act<T>(lsb_to_float(raw.v[u][x]), v_act);
+                    if (c + x < cols)
+                        v_sh[j * cols + c + x] = (ones && col0 + c + x == V) ? 1.f
+                                                                             : scan_act<T>(lsb_to_float(raw.v[u][x]), v_act);
             }
         }
     };
@@ -206,11 +219,14 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
             const int j = i / D, d = i % D;
             const T* row = proj + (size_t)(base + j) * ld;
             const int at = j * Dp + chan_slot(d, PER, split);
-            if (MODE != 1) q_sh[at] = scan_act<T>(lsb_to_float(row[q_off + h * D + d]), q_act);
+            if (MODE != 1) q_sh[at] = scan_act<T>(lsb_to_float(row[q_off + h * D + d]), q_act) * q_scale;
             const float z = lsb_to_float(row[k_off + h * D + d]);
             if (gate == 0) {
                 a_sh[at] = fixed;
                 b_sh[at] = scan_act<T>(z, k_act);
+            } else if (gate == 2) {
+                a_sh[at] = g_keep[(size_t)(base + j) * heads + h];
+                b_sh[at] = g_write[(size_t)(base + j) * heads + h] * scan_act<T>(z, k_act);
             } else {
                 const float lo = floor_[h * D + d];
                 const float sg = scan_sigmoid<T>(z + (f_bias ? f_bias[h * D + d] : 0.f));
@@ -221,7 +237,8 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
         }
         for (int i = threadIdx.x; i < n * cols; i += kScanThreads) {
             const int j = i / cols, c = col0 + i % cols;
-            v_sh[i] = c < V ? scan_act<T>(lsb_to_float(proj[(size_t)(base + j) * ld + v_off + h * V + c]), v_act) : 0.f;
+            v_sh[i] = c < V ? scan_act<T>(lsb_to_float(proj[(size_t)(base + j) * ld + v_off + h * V + c]), v_act)
+                            : (ones && c == V) ? 1.f : 0.f;
         }
     };
 
@@ -233,7 +250,7 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
     for (int base = t0; base < t1; base += kChunk) {
         const int n = min(kChunk, t1 - base);
         __syncthreads();                                    // the chunk before has been walked
-        if (fits) stage(n);
+        if (fits) stage(base, n);
         else stage_plain(base, n);
         __syncthreads();
         if (fits && base + kChunk < t1) fetch(base + kChunk, min(kChunk, t1 - base - kChunk));
@@ -279,7 +296,7 @@ linear_scan_kernel(const T* __restrict__ proj, long long ld, int q_off, int k_of
             if (MODE != 1) {
                 float acc = acc0 + acc1;
                 for (int o = split >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                if (part == 0 && live) out[(size_t)(base + j) * heads * V + h * V + col] = acc;
+                if (part == 0 && live) out[(size_t)(base + j) * heads * Vs + h * Vs + col] = acc;
             }
 #pragma unroll
             for (int x = 0; x < PER / 4; ++x) { qc[x] = qn[x]; ac[x] = an[x]; bc[x] = bn[x]; }
@@ -348,6 +365,8 @@ static inline void scan_shape(int D, int* split, int* per) {
 
 LSB_API int lsb_linear_scan_supported(int D) { return D > 0 && D <= 32 * 32; }
 
+// g_keep, g_write [tokens, heads]: gate 2 only.  ones: see above.  The state is [slots, heads, V + ones, D],
+// out [tokens, heads, V + ones].
 // seg_len > 0 with scratch given: portions longer than a segment are walked in segments side by
 // side (see above); seg_state [requests * max_segs, heads, V, D] and seg_decay [requests * max_segs,
 // heads, D] with max_segs = ceil(max_q_len / seg_len).
@@ -356,18 +375,22 @@ LSB_API int lsb_linear_scan(const void* proj, int dtype, long long ld, int q_off
                             const float* floor_, int q_act, int k_act, int v_act, float* state,
                             int n_slots, const int* q_start, const int* table_rows, int n_requests,
                             float* out, int seg_len, int max_q_len, float* seg_state, float* seg_decay,
+                            const float* g_keep, const float* g_write, int ones, float q_scale,
                             cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (heads <= 0 || V <= 0 || !lsb_linear_scan_supported(D) || heads > 65535 || n_requests > 65535)
         return (int)cudaErrorInvalidValue;
-    if ((gate == 0 && !decay) || (gate == 1 && !floor_) || gate < 0 || gate > 1) return (int)cudaErrorInvalidValue;
+    if ((gate == 0 && !decay) || (gate == 1 && !floor_) || (gate == 2 && (!g_keep || !g_write)) || gate < 0 || gate > 2)
+        return (int)cudaErrorInvalidValue;
+    ones = ones ? 1 : 0;
+    const int Vs = V + ones;
     int split, per;
     scan_shape(D, &split, &per);
     const int cols = kScanThreads / split;
     const bool segmented = seg_len > 0 && seg_state && seg_decay && max_q_len > seg_len;
     const int max_segs = segmented ? (max_q_len + seg_len - 1) / seg_len : 1;
     if ((long long)n_requests * max_segs > 65535) return (int)cudaErrorInvalidValue;
-    dim3 grid((V + cols - 1) / cols, heads, n_requests * max_segs);
+    dim3 grid((Vs + cols - 1) / cols, heads, n_requests * max_segs);
     const size_t smem = (size_t)kChunk * (3 * (per + 4) * split + cols) * sizeof(float);
     // 16-byte loads of eight channels: every group of eight must start on a 16-byte boundary
     const int esz = dtype == LSB_F32 ? 4 : 2, al = 16 / esz;
@@ -383,7 +406,7 @@ LSB_API int lsb_linear_scan(const void* proj, int dtype, long long ld, int q_off
         int rc = lsb_launch(linear_scan_kernel<T, PER, MODE>, grid, dim3(kScanThreads), smem, stream, 1, \
                           (const T*)proj, ld, q_off, k_off, v_off, heads, D, V, gate, decay, f_bias,  \
                           floor_, q_act, k_act, v_act, state, n_slots, q_start, table_rows, out, split, vec, \
-                          seg_len, max_segs, seg_state, seg_decay);                                   \
+                          seg_len, max_segs, seg_state, seg_decay, g_keep, g_write, ones, q_scale);   \
         if (rc) return rc;                                                                            \
     } while (0)
 #define LSB_SCAN_PER(MODE)                                                                            \
@@ -397,10 +420,10 @@ LSB_API int lsb_linear_scan(const void* proj, int dtype, long long ld, int q_off
             LSB_SCAN_PER(0);
         } else {
             LSB_SCAN_PER(1);
-            const size_t per_state = (size_t)heads * V * D;
+            const size_t per_state = (size_t)heads * Vs * D;
             const int blocks = (int)((per_state + 255) / 256 < 1024 ? (per_state + 255) / 256 : 1024);
             int rc = lsb_launch(scan_chain_kernel, dim3(blocks, n_requests), dim3(256), 0, stream, 1, state, n_slots,
-                                seg_state, (const float*)seg_decay, q_start, table_rows, heads, D, V, seg_len, max_segs);
+                                seg_state, (const float*)seg_decay, q_start, table_rows, heads, D, Vs, seg_len, max_segs);
             if (rc) return rc;
             LSB_SCAN_PER(2);
         }

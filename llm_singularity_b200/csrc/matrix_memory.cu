@@ -1,0 +1,127 @@
+// The gates and the output step of a matrix memory with an exponential input gate (the mLSTM
+// cell), around the walk of csrc/linear_scan.cu.  Per head and token, from the raw gate
+// projections zi, zf (32-bit) and their biases:
+//
+//     i = cap * tanh((zi + bi) / cap)               f = logsigmoid(cap * tanh((zf + bf) / cap))
+//     m_t = max(f + m_(t-1), i)                     (m starts at 0 when a request begins)
+//     keep_t = exp(f + m_(t-1) - m_t)   write_t = exp(i - m_t)   floor_t = exp(-m_t)
+//
+// keep and write are what the walk multiplies the state and the incoming k v^T by (the same for
+// every channel of the head); with a value column of ones riding along, the walk also carries the
+// normaliser n and hands back n . q beside S^T q.  The output step then forms
+//
+//     o = S^T q / (max(|n . q|, floor_t) + 1e-6)
+//     y = o / sqrt(mean(o^2) + eps) * w[head, :] * sigmoid(gate)         (mean over the head's values)
+//
+// The chain of maxima is walked in order by one lane per (request, head), with exactly the
+// arithmetic above, while the transcendental functions on either side of it are spread over the
+// warp.  Everything here is 32-bit.
+#include "common.cuh"
+
+LSB_DEFINE_STATUS()
+
+constexpr int kGateChunk = 128;       // tokens staged at a time (four per lane)
+
+__device__ __forceinline__ float mm_logsigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+// raw [tokens, 2 * heads]: zi of every head, then zf.  gates [3][tokens][heads]: keep, write, floor.
+// m_state [slots, heads].
+__global__ void __launch_bounds__(32)
+memory_gates_kernel(const float* __restrict__ raw, const float* __restrict__ i_bias, const float* __restrict__ f_bias,
+                    float cap, float* __restrict__ m_state, int n_slots, const int* __restrict__ q_start,
+                    const int* __restrict__ table_rows, float* __restrict__ gates, int tokens, int heads) {
+    __shared__ float i_sh[kGateChunk], f_sh[kGateChunk], m_sh[kGateChunk + 1];
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int h = blockIdx.x, r = blockIdx.y, lane = threadIdx.x;
+    const int t0 = q_start[r], t1 = q_start[r + 1];
+    const int slot = table_rows[r];
+    if (slot < 0 || slot >= n_slots) {
+        if (lane == 0) lsb_set_status(LSB_BAD_ROW);
+        return;
+    }
+    float m = m_state[(size_t)slot * heads + h];
+    const float bi = i_bias ? i_bias[h] : 0.f, bf = f_bias ? f_bias[h] : 0.f;
+    const size_t plane = (size_t)tokens * heads;
+    for (int base = t0; base < t1; base += kGateChunk) {
+        const int n = min(kGateChunk, t1 - base);
+        for (int j = lane; j < n; j += 32) {
+            const float* z = raw + (size_t)(base + j) * 2 * heads;
+            i_sh[j] = cap * tanhf((z[h] + bi) / cap);
+            f_sh[j] = mm_logsigmoid(cap * tanhf((z[heads + h] + bf) / cap));
+        }
+        __syncwarp();
+        if (lane == 0) {
+            m_sh[0] = m;
+            float cur = m;
+#pragma unroll 8
+            for (int j = 0; j < n; ++j) {
+                cur = fmaxf(f_sh[j] + cur, i_sh[j]);
+                m_sh[j + 1] = cur;
+            }
+        }
+        __syncwarp();
+        for (int j = lane; j < n; j += 32) {
+            const float before = m_sh[j], now = m_sh[j + 1];
+            const size_t at = (size_t)(base + j) * heads + h;
+            gates[at] = expf(f_sh[j] + before - now);
+            gates[plane + at] = expf(i_sh[j] - now);
+            gates[2 * plane + at] = expf(-now);
+        }
+        m = m_sh[n];
+        __syncwarp();
+    }
+    if (lane == 0) m_state[(size_t)slot * heads + h] = m;
+}
+
+LSB_API int lsb_memory_gates(const float* raw, const float* i_bias, const float* f_bias, float cap, float* m_state,
+                             int n_slots, const int* q_start, const int* table_rows, int n_requests, float* gates,
+                             int tokens, int heads, cudaStream_t stream) {
+    if (n_requests <= 0 || tokens <= 0) return 0;
+    if (heads <= 0 || heads > 65535 || n_requests > 65535 || !(cap > 0.f)) return (int)cudaErrorInvalidValue;
+    return lsb_launch(memory_gates_kernel, dim3(heads, n_requests), dim3(32), 0, stream, 1, raw, i_bias, f_bias, cap,
+                      m_state, n_slots, q_start, table_rows, gates, tokens, heads);
+}
+
+// walked [tokens, heads, V + 1]: S^T q in the first V columns of a head, n . q in the last.
+// floor_ [tokens, heads].  One warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(128)
+memory_output_kernel(const float* __restrict__ walked, const float* __restrict__ floor_, const float* __restrict__ weight,
+                     const T* __restrict__ gate, long long gate_stride, T* __restrict__ out, int tokens, int heads, int V,
+                     float eps) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)tokens * heads) return;
+    const int t = (int)(item / heads), h = (int)(item % heads);
+    const float* w = walked + (size_t)item * (V + 1);
+    const float denom = fmaxf(fabsf(w[V]), floor_[item]) + 1e-6f;
+    float ss = 0.f;
+    for (int c = lane; c < V; c += 32) {
+        const float o = w[c] / denom;
+        ss += o * o;
+    }
+    const float inv = rsqrtf(lsb_warp_sum(ss) / (float)V + eps);
+    const T* g = gate ? gate + (size_t)t * gate_stride + (size_t)h * V : nullptr;
+    T* y = out + ((size_t)t * heads + h) * V;
+    for (int c = lane; c < V; c += 32) {
+        float v = w[c] / denom * inv * weight[h * V + c];
+        if (g) v *= 1.f / (1.f + expf(-lsb_to_float(g[c])));
+        y[c] = lsb_from_float<T>(v);
+    }
+}
+
+LSB_API int lsb_memory_output(const float* walked, const float* floor_, const float* weight, const void* gate,
+                              long long gate_stride, void* out, int dtype, int tokens, int heads, int V, float eps,
+                              cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (heads <= 0 || V <= 0) return (int)cudaErrorInvalidValue;
+    const long long items = (long long)tokens * heads;
+    const int blocks = (int)((items + 3) / 4);
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(memory_output_kernel<T>, dim3(blocks), dim3(128), 0, stream, 1, walked,
+                                                floor_, weight, (const T*)gate, gate_stride, (T*)out, tokens, heads, V,
+                                                eps));
+    return 0;
+}

@@ -1,0 +1,154 @@
+// Rows of a residual stream whose sublayers are normed on both sides:
+//
+//     x <- x + mult * unit(y) * w_post  [+ step]        out = unit(x) * w_next
+//
+// with unit(z) = z / sqrt(mean(z^2) + eps).  One kernel does the norm behind a sublayer, the sum
+// into the 32-bit stream, an optional vector added to every row (the step vector of a pass through
+// looped layers) and the norm in front of the next sublayer; each of the three is optional.  The
+// gathered form does the same for selected rows and leaves the stream alone (the rows whose
+// logits are wanted).  All arithmetic is 32-bit; y and out are in the compute dtype.
+//
+// The second kernel is the meeting point of mixers that run side by side on one input:
+// out = (1 / n) * sum_b unit(y_b) * w_b, each branch normed over the row with its own weight.
+//
+// One thread block per row; the row waits in shared memory between the passes.
+#include "common.cuh"
+
+LSB_DEFINE_STATUS()
+
+constexpr int kRowThreads = 256;
+
+template <typename T, bool GATHER>
+__global__ void __launch_bounds__(kRowThreads)
+stream_norm_kernel(float* __restrict__ residual, const T* __restrict__ y, const float* __restrict__ post_w,
+                   float post_eps, float mult, const float* __restrict__ step, const int* __restrict__ rows,
+                   const float* __restrict__ next_w, float next_eps, T* __restrict__ out, int hidden,
+                   int n_rows_total) {
+    extern __shared__ float row_sh[];
+    __shared__ float scratch[33];
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int r_out = blockIdx.x;
+    int r_in = r_out;
+    if (GATHER) {
+        r_in = rows[r_out];
+        if (r_in < 0 || r_in >= n_rows_total) {
+            if (threadIdx.x == 0) lsb_set_status(LSB_BAD_ROW);
+            if (out)
+                for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)r_out * hidden + i] = lsb_from_float<T>(0.f);
+            return;
+        }
+    }
+    float* res = residual + (size_t)r_in * hidden;
+    const T* yr = y ? y + (size_t)r_in * hidden : nullptr;
+    float inv_y = 1.f;
+    if (yr && post_w) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < hidden; i += kRowThreads) {
+            const float v = lsb_to_float(yr[i]);
+            row_sh[i] = v;
+            ss += v * v;
+        }
+        ss = lsb_block_sum(ss, scratch);
+        inv_y = rsqrtf(ss / (float)hidden + post_eps);
+    }
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += kRowThreads) {
+        float x = res[i];
+        if (yr) x += post_w ? mult * (row_sh[i] * inv_y * post_w[i]) : mult * lsb_to_float(yr[i]);
+        if (step) x += step[i];
+        if (!GATHER && (yr || step)) res[i] = x;
+        row_sh[i] = x;
+        ss += x * x;
+    }
+    if (!out) return;
+    ss = lsb_block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)hidden + next_eps);
+    T* o = out + (size_t)r_out * hidden;
+    for (int i = threadIdx.x; i < hidden; i += kRowThreads) o[i] = lsb_from_float<T>(row_sh[i] * inv * next_w[i]);
+}
+
+// y, post_w, step, next_w / out may each be null (post_w null with y given: a plain sum of mult * y).
+// rows null: every row of the stream, in place; else the rows named, the stream untouched.
+LSB_API int lsb_stream_norm(float* residual, const void* y, const float* post_w, float post_eps, float mult,
+                            const float* step, const int* rows, int n_rows, const float* next_w, float next_eps,
+                            void* out, int dtype, int n_rows_total, int hidden, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (hidden <= 0 || (out && !next_w)) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+#define LSB_STREAM_NORM(G)                                                                            \
+    do {                                                                                              \
+        if (smem > 48 * 1024) {                                                                       \
+            int rc = (int)cudaFuncSetAttribute(stream_norm_kernel<T, G>,                              \
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (rc) return rc;                                                                        \
+        }                                                                                             \
+        return lsb_launch(stream_norm_kernel<T, G>, dim3(n_rows), dim3(kRowThreads), smem, stream, 1, residual, \
+                          (const T*)y, post_w, post_eps, mult, step, rows, next_w, next_eps, (T*)out, hidden,  \
+                          n_rows_total);                                                              \
+    } while (0)
+    LSB_DISPATCH_DTYPE(dtype, {
+        if (rows) LSB_STREAM_NORM(true);
+        else LSB_STREAM_NORM(false);
+    });
+#undef LSB_STREAM_NORM
+    return 0;
+}
+
+constexpr int kMaxBranches = 4;
+struct Branches {
+    const void* y[kMaxBranches];
+    const float* w[kMaxBranches];
+    int n;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+branch_mean_kernel(Branches br, float eps, T* __restrict__ out, int hidden) {
+    __shared__ float scratch[33];
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const size_t base = (size_t)blockIdx.x * hidden;
+    float inv[kMaxBranches];
+#pragma unroll
+    for (int b = 0; b < kMaxBranches; ++b) {
+        inv[b] = 0.f;
+        if (b < br.n) {
+            const T* yb = (const T*)br.y[b] + base;
+            float ss = 0.f;
+            for (int i = threadIdx.x; i < hidden; i += kRowThreads) {
+                const float v = lsb_to_float(yb[i]);
+                ss += v * v;
+            }
+            ss = lsb_block_sum(ss, scratch);
+            inv[b] = rsqrtf(ss / (float)hidden + eps);
+        }
+    }
+    const float share = 1.f / (float)br.n;
+    for (int i = threadIdx.x; i < hidden; i += kRowThreads) {
+        float s = 0.f;
+#pragma unroll
+        for (int b = 0; b < kMaxBranches; ++b)
+            if (b < br.n) s += lsb_to_float(((const T*)br.y[b])[base + i]) * inv[b] * br.w[b][i];
+        out[base + i] = lsb_from_float<T>(s * share);
+    }
+}
+
+LSB_API int lsb_branch_max() { return kMaxBranches; }
+
+// ys, ws: n pointers each (rows of the branches in the compute dtype, their 32-bit weights).
+LSB_API int lsb_branch_mean(const void* const* ys, const float* const* ws, int n, float eps, void* out, int dtype,
+                            int n_rows, int hidden, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (n <= 0 || n > kMaxBranches || hidden <= 0) return (int)cudaErrorInvalidValue;
+    Branches br;
+    br.n = n;
+    for (int b = 0; b < kMaxBranches; ++b) {
+        br.y[b] = b < n ? ys[b] : nullptr;
+        br.w[b] = b < n ? ws[b] : nullptr;
+    }
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(branch_mean_kernel<T>, dim3(n_rows), dim3(kRowThreads), 0, stream, 1,
+                                                br, eps, (T*)out, hidden));
+    return 0;
+}

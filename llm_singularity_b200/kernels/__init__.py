@@ -233,8 +233,8 @@ def random_normal(out: torch.Tensor, key: int, mean: float, scale: float) -> Non
           ctypes.c_ulonglong(key & ((1 << 64) - 1)), _f(mean), _f(scale), _stream(out))
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, :] = float(table[ids[t], :])."""
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t, :] = float(table[ids[t], :]) * scale."""
     _req(table, "table", dim=2)
     _req(ids, "ids", torch.int32, 1)
     _req(out, "out", torch.float32, 2)
@@ -242,7 +242,7 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None
         raise KernelError(f"embedding: out is {tuple(out.shape)}, expected "
                           f"{(ids.shape[0], table.shape[1])}")
     _call("embedding", "lsb_embedding", _p(table), _i(_dt(table)), _p(ids), _p(out),
-          _i(ids.shape[0]), _i(table.shape[1]), _i(table.shape[0]), _stream(out))
+          _i(ids.shape[0]), _i(table.shape[1]), _i(table.shape[0]), _f(scale), _stream(out))
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
@@ -883,7 +883,7 @@ def token_side_gate(g: torch.Tensor, table: torch.Tensor, token_ids: torch.Tenso
 
 
 # ------------------------------------------------------------------ linear recurrence
-SCAN_GATES = {"fixed_decay": 0, "forget": 1}
+SCAN_GATES = {"fixed_decay": 0, "forget": 1, "given": 2}
 _SCAN_ACTS = {"none": 0, "silu": 1}
 SCAN_SEGMENT = 128              # tokens of a segment when long portions are walked in segments (0: never)
 
@@ -891,19 +891,33 @@ SCAN_SEGMENT = 128              # tokens of a segment when long portions are wal
 def linear_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, key_dim: int,
                 value_dim: int, gate: str, decay: Optional[torch.Tensor], f_bias: Optional[torch.Tensor],
                 floor: Optional[torch.Tensor], q_act: str, k_act: str, v_act: str, state: torch.Tensor,
-                ctx, out: torch.Tensor) -> None:
+                ctx, out: torch.Tensor, keep: Optional[torch.Tensor] = None, write: Optional[torch.Tensor] = None,
+                ones: bool = False, q_scale: float = 1.0) -> None:
     """S <- diag(a) S + b v^T, o = S^T q per head and token, each request from its slot's state
     (``state`` [slots, heads, value_dim, key_dim] 32-bit, updated in place); ``proj`` [T, columns] holds
     the projections of q at ``q_off``, of k (or the forget gate) at ``k_off`` and of v at ``v_off``;
-    ``out`` [T, heads * value_dim] 32-bit."""
+    ``out`` [T, heads * value_dim] 32-bit.
+
+    Gate "given": ``keep`` and ``write`` (32-bit [T, heads]) are a and the factor of b for every channel
+    of a head.  ``ones``: a value column of ones rides along behind each head's ``value_dim`` columns
+    (state and out then have ``value_dim + 1`` columns a head, the last one of out being the
+    running sum of b dotted with q).  ``q_scale`` multiplies q."""
     _req(proj, "proj", dim=2)
     _req(state, "state", torch.float32, 4)
     _req(out, "out", torch.float32, 2)
     T, ld = proj.shape
-    if state.shape[1:] != (heads, value_dim, key_dim) or out.shape != (T, heads * value_dim) or ctx.n_tokens != T:
+    cols = value_dim + (1 if ones else 0)
+    if state.shape[1:] != (heads, cols, key_dim) or out.shape != (T, heads * cols) or ctx.n_tokens != T:
         raise KernelError("linear_scan: state, out or the step do not fit the sizes")
     if max(q_off, k_off) + heads * key_dim > ld or v_off + heads * value_dim > ld or min(q_off, k_off, v_off) < 0:
         raise KernelError("linear_scan: a projection lies outside the rows of proj")
+    if gate == "given" and (keep is None or write is None):
+        raise KernelError("linear_scan: given gates need keep and write")
+    for name, t in (("keep", keep), ("write", write)):
+        if t is not None:
+            _req(t, name, torch.float32, 2)
+            if t.shape != (T, heads):
+                raise KernelError(f"linear_scan: {name} must be [tokens, heads]")
     for name, t, n in (("decay", decay, heads), ("f_bias", f_bias, heads * key_dim), ("floor", floor, heads * key_dim)):
         if t is not None:
             _req(t, name, torch.float32, 1)
@@ -917,13 +931,13 @@ def linear_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: i
     if SCAN_SEGMENT and ctx.max_q_len >= 2 * SCAN_SEGMENT and ctx.n_requests <= 8:
         seg = SCAN_SEGMENT
         n = ctx.n_requests * -(-ctx.max_q_len // seg)
-        seg_state = torch.empty(n * heads * value_dim * key_dim, dtype=torch.float32, device=proj.device)
+        seg_state = torch.empty(n * heads * cols * key_dim, dtype=torch.float32, device=proj.device)
         seg_decay = torch.empty(n * heads * key_dim, dtype=torch.float32, device=proj.device)
     _call("linear_scan", "lsb_linear_scan", _p(proj), _i(_dt(proj)), _ll(ld), _i(q_off), _i(k_off), _i(v_off),
           _i(heads), _i(key_dim), _i(value_dim), _i(SCAN_GATES[gate]), _p(decay), _p(f_bias), _p(floor),
           _i(_SCAN_ACTS[q_act]), _i(_SCAN_ACTS[k_act]), _i(_SCAN_ACTS[v_act]), _p(state), _i(state.shape[0]),
           _p(ctx.q_start), _p(ctx.table_rows), _i(ctx.n_requests), _p(out), _i(seg), _i(ctx.max_q_len),
-          _p(seg_state), _p(seg_decay), _stream(out))
+          _p(seg_state), _p(seg_decay), _p(keep), _p(write), _i(1 if ones else 0), _f(q_scale), _stream(out))
 
 
 # --------------------------------------------------------------------- latent attention
@@ -1033,6 +1047,180 @@ def latent_attention(qf: torch.Tensor, ctx, cache, kv_rank: int, rot_dim: int, s
           _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(out), _i(ctx.n_requests),
           _i(ctx.max_q_len), _i(H), _i(kv_rank), _i(rot_dim), _i(cache.page_size), _i(cache.pages.shape[0]),
           _f(scale), _stream(out))
+
+
+# ------------------------------------------------- a stream whose sublayers are normed on both sides
+def stream_norm(residual: torch.Tensor, y: Optional[torch.Tensor], post_weight: Optional[torch.Tensor],
+                post_eps: float, mult: float, step: Optional[torch.Tensor], rows: Optional[torch.Tensor],
+                next_weight: Optional[torch.Tensor], next_eps: float, out: Optional[torch.Tensor]) -> None:
+    """residual += mult * unit(y) * post_weight (+ step, one vector for every row); out = unit(residual) *
+    next_weight; unit(z) = z / sqrt(mean(z^2) + eps).  Every piece is optional (``post_weight`` None
+    with ``y`` given: a plain sum of mult * y).  ``rows`` (int32): only those rows, into ``out``
+    [len(rows), H], the stream untouched."""
+    _req(residual, "residual", torch.float32, 2)
+    T, H = residual.shape
+    n = T if rows is None else rows.shape[0]
+    if rows is not None:
+        _req(rows, "rows", torch.int32, 1)
+    dtype = None
+    for name, t in (("y", y), ("out", out)):
+        if t is not None:
+            _req(t, name, dtype, 2)
+            dtype = t.dtype
+    if y is not None and y.shape != (T, H):
+        raise KernelError("stream_norm: y has another shape than the stream")
+    if out is not None and (out.shape != (n, H) or next_weight is None):
+        raise KernelError("stream_norm: out must be [rows, H] and needs the weight of its norm")
+    for name, t in (("post_weight", post_weight), ("step", step), ("next_weight", next_weight)):
+        if t is not None:
+            _req(t, name, torch.float32, 1)
+            if t.shape[0] != H:
+                raise KernelError(f"stream_norm: {name} must have {H} entries")
+    if dtype is None:
+        if step is None:
+            return
+        dtype = torch.float32
+    _call("sandwich", "lsb_stream_norm", _p(residual), _p(y), _p(post_weight), _f(post_eps), _f(mult), _p(step),
+          _p(rows), _i(n), _p(next_weight), _f(next_eps), _p(out), _i(_F32 if dtype == torch.float32 else _BF16),
+          _i(T), _i(H), _stream(residual))
+
+
+def branch_mean(ys, weights, eps: float, out: torch.Tensor) -> None:
+    """out = mean over the branches b of unit(ys[b]) * weights[b], row by row."""
+    _req(out, "out", dim=2)
+    n = len(ys)
+    if n == 0 or n != len(weights) or n > _lib("sandwich").lsb_branch_max():
+        raise KernelError(f"branch_mean: {n} branches with {len(weights)} weights")
+    for y, w in zip(ys, weights):
+        _req(y, "branch", out.dtype, 2)
+        _req(w, "branch weight", torch.float32, 1)
+        if y.shape != out.shape or w.shape[0] != out.shape[1]:
+            raise KernelError("branch_mean: a branch or its weight does not fit out")
+    yp = (ctypes.c_void_p * n)(*[_p(y).value for y in ys])
+    wp = (ctypes.c_void_p * n)(*[_p(w).value for w in weights])
+    _call("sandwich", "lsb_branch_mean", yp, wp, _i(n), _f(eps), _p(out), _i(_dt(out)), _i(out.shape[0]),
+          _i(out.shape[1]), _stream(out))
+
+
+# ------------------------------------------ attention with key and value sizes of their own
+def _check_kv_cache(cache, nkv: int, dk: int, dv: int, dtype) -> None:
+    for name, d in (("k_pages", dk), ("v_pages", dv)):
+        t = _req(getattr(cache, name), name, dtype, 4)
+        if t.shape[1:] != (nkv, cache.page_size, d):
+            raise KernelError(f"{name} is {tuple(t.shape)}, expected [pages, {nkv}, {cache.page_size}, {d}]")
+    _req(cache.block_table, "block_table", torch.int32, 2)
+
+
+def attention_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, nh: int, nkv: int, dk: int, dv: int,
+                   ctx, cache, q_out: torch.Tensor, *, q_bias=None, k_bias=None, v_bias=None, q_norm=None,
+                   k_norm=None, norm_eps: float = 0.0, temp_coef: float = 0.0, temp_every: int = 0,
+                   inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0, pairing: str = "half",
+                   store: bool = True) -> None:
+    """From the rows of ``proj`` (q at ``q_off``, k at ``k_off``, v at ``v_off``) to queries in ``q_out``
+    [T, nh * dk] and keys and values in this step's cache places: biases, a norm per head of q and k
+    (one weight of head size each), the query temperature ``1 + coef * ln(floor((pos + 1) / every) + 1)``
+    and the rotation of the first ``rotary_dim`` dims, each if given."""
+    _req(proj, "proj", dim=2)
+    _req(q_out, "q_out", proj.dtype, 2)
+    T, ld = proj.shape
+    if ctx.n_tokens != T or q_out.shape != (T, nh * dk):
+        raise KernelError("attention_prep: proj, q_out and the step disagree")
+    if min(q_off, k_off, v_off) < 0 or q_off + nh * dk > ld or k_off + nkv * dk > ld or v_off + nkv * dv > ld:
+        raise KernelError("attention_prep: a projection lies outside the rows of proj")
+    if dk > _lib("attention_prep").lsb_attention_prep_max_dim():
+        raise KernelError(f"attention_prep: key size {dk} is not supported")
+    for name, t, n in (("q_bias", q_bias, nh * dk), ("k_bias", k_bias, nkv * dk), ("v_bias", v_bias, nkv * dv),
+                       ("q_norm", q_norm, dk), ("k_norm", k_norm, dk)):
+        if t is not None:
+            _req(t, name, torch.float32, 1)
+            if t.shape[0] != n:
+                raise KernelError(f"attention_prep: {name} must have {n} entries")
+    if rotary_dim:
+        _req(inv_freq, "inv_freq", torch.float32, 1)
+        if rotary_dim % 2 or rotary_dim > dk or inv_freq.shape[0] != rotary_dim // 2:
+            raise KernelError("attention_prep: rotary_dim must be even, at most the key size, with rotary_dim / 2 "
+                              "frequencies")
+    _check_kv_cache(cache, nkv, dk, dv, proj.dtype)
+    _call("attention_prep", "lsb_attention_prep", _p(proj), _i(_dt(proj)), _ll(ld), _i(q_off), _i(k_off), _i(v_off),
+          _i(T), _i(nh), _i(nkv), _i(dk), _i(dv), _p(q_bias), _p(k_bias), _p(v_bias), _p(q_norm), _p(k_norm),
+          _f(norm_eps), _f(temp_coef), _i(temp_every), _p(inv_freq if rotary_dim else None), _i(rotary_dim),
+          _i(_PAIRINGS[pairing]), _p(ctx.positions), _p(ctx.token_req), _p(ctx.table_rows), _p(cache.block_table),
+          _i(cache.block_table.shape[1]), _p(q_out), _p(cache.k_pages), _p(cache.v_pages), _i(cache.page_size),
+          _i(cache.k_pages.shape[0]), _i(1 if store else 0), _stream(proj))
+
+
+def attention_dv(q: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, ctx, cache, scale: float, window: int,
+                 chunk: int, gate: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """Softmax attention of this step's queries ``q`` [T, nh * dk] over their requests' cached keys (size
+    dk) and values (size dv): a query at position p sees ``[lo, p]`` with lo the larger of
+    ``p - window + 1`` (window > 0) and the start of p's chunk of ``chunk`` positions (chunk > 0).
+    ``gate`` [T, nh * dv] (rows may be strided): out *= sigmoid(gate)."""
+    _req(q, "q", dim=2)
+    _req(out, "out", q.dtype, 2)
+    T = q.shape[0]
+    if q.shape[1] != nh * dk or out.shape != (T, nh * dv) or ctx.n_tokens != T:
+        raise KernelError("attention_dv: q, out and the step disagree")
+    if nkv <= 0 or nh % nkv:
+        raise KernelError(f"attention_dv: {nh} heads cannot share {nkv} kv heads")
+    if max(dk, dv) > _lib("attention_dv").lsb_attention_dv_max_dim():
+        raise KernelError(f"attention_dv: head sizes {dk}, {dv} are not supported")
+    gate_stride = 0
+    if gate is not None:
+        _req(gate, "gate", q.dtype, 2, contiguous=False)
+        if gate.shape != (T, nh * dv) or gate.stride(1) != 1:
+            raise KernelError("attention_dv: the gate must be [T, heads * value size] with unit column stride")
+        gate_stride = gate.stride(0)
+    _check_kv_cache(cache, nkv, dk, dv, q.dtype)
+    _call("attention_dv", "lsb_attention_dv_generic", _p(q), _p(cache.k_pages), _p(cache.v_pages), _p(ctx.q_start),
+          _p(ctx.kv_len), _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(gate),
+          _ll(gate_stride), _p(out), _i(_dt(q)), _i(ctx.n_requests), _i(ctx.max_q_len), _i(nh), _i(nkv), _i(dk),
+          _i(dv), _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale), _i(window), _i(chunk), _stream(out))
+
+
+# -------------------------------------------------- matrix memory with an exponential input gate
+def memory_gates(raw: torch.Tensor, i_bias: Optional[torch.Tensor], f_bias: Optional[torch.Tensor], cap: float,
+                 m_state: torch.Tensor, ctx, gates: torch.Tensor) -> None:
+    """``raw`` [T, 2 * heads] 32-bit holds the input-gate and then the forget-gate projections.  With
+    i = cap * tanh((zi + bi) / cap), f = logsigmoid(cap * tanh((zf + bf) / cap)) and the running
+    maximum m_t = max(f + m_(t-1), i) (per request and head, carried in ``m_state`` [slots, heads]),
+    ``gates`` [3, T, heads] receives exp(f + m_(t-1) - m_t), exp(i - m_t) and exp(-m_t)."""
+    _req(raw, "raw", torch.float32, 2)
+    _req(m_state, "m_state", torch.float32, 2)
+    _req(gates, "gates", torch.float32, 3)
+    T, heads = raw.shape[0], m_state.shape[1]
+    if raw.shape[1] != 2 * heads or gates.shape != (3, T, heads) or ctx.n_tokens != T:
+        raise KernelError("memory_gates: raw, m_state, gates and the step disagree")
+    for name, t in (("i_bias", i_bias), ("f_bias", f_bias)):
+        if t is not None:
+            _req(t, name, torch.float32, 1)
+            if t.shape[0] != heads:
+                raise KernelError(f"memory_gates: {name} must have {heads} entries")
+    _call("matrix_memory", "lsb_memory_gates", _p(raw), _p(i_bias), _p(f_bias), _f(cap), _p(m_state),
+          _i(m_state.shape[0]), _p(ctx.q_start), _p(ctx.table_rows), _i(ctx.n_requests), _p(gates), _i(T), _i(heads),
+          _stream(gates))
+
+
+def memory_output(walked: torch.Tensor, floor: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor],
+                  eps: float, out: torch.Tensor) -> None:
+    """``walked`` [T, heads * (V + 1)] 32-bit: per head S^T q in V columns and n . q in the last;
+    ``floor`` [T, heads].  o = S^T q / (max(|n . q|, floor) + 1e-6); out = unit(o) per head * weight
+    [heads * V] * sigmoid(gate)."""
+    _req(walked, "walked", torch.float32, 2)
+    _req(floor, "floor", torch.float32, 2)
+    _req(weight, "weight", torch.float32, 1)
+    _req(out, "out", dim=2)
+    T, heads = floor.shape
+    V = out.shape[1] // max(heads, 1)
+    if out.shape != (T, heads * V) or walked.shape != (T, heads * (V + 1)) or weight.shape[0] != heads * V:
+        raise KernelError("memory_output: shapes disagree")
+    gate_stride = 0
+    if gate is not None:
+        _req(gate, "gate", out.dtype, 2, contiguous=False)
+        if gate.shape != out.shape or gate.stride(1) != 1:
+            raise KernelError("memory_output: the gate must have out's shape and unit column stride")
+        gate_stride = gate.stride(0)
+    _call("matrix_memory", "lsb_memory_output", _p(walked), _p(floor), _p(weight), _p(gate), _ll(gate_stride),
+          _p(out), _i(_dt(out)), _i(T), _i(heads), _i(V), _f(eps), _stream(out))
 
 
 # ------------------------------------------------------------------------ routed experts

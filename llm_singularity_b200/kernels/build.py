@@ -45,6 +45,10 @@ SOURCES: Dict[str, object] = {          # library -> its source file (or files)
     "latent": "latent.cu",
     "latent_tc": "latent_tc.cu",
     "moe": "moe.cu",
+    "sandwich": "sandwich.cu",
+    "attention_prep": "attention_prep.cu",
+    "attention_dv": "attention_dv.cu",
+    "matrix_memory": "matrix_memory.cu",
     "sampling": "sampling.cu",
     "random_init": "random_init.cu",
     # host code only: pools, block tables, prefix tree; scheduler

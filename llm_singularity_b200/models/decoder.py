@@ -17,7 +17,7 @@ import torch
 from ..config.specs import ModelSpec
 from ..parts import BLOCKS
 from ..parts.base import ParamSpec, Part, Runtime
-from ..parts.embedding import Embedding, LMHead
+from ..parts.embedding import Embedding, LMHead, StepVectors
 
 
 class DecoderModel:
@@ -27,7 +27,12 @@ class DecoderModel:
         self.embedding = Embedding(spec.embedding, rt)
         self.blocks: List[Part] = [BLOCKS.build(b, rt) for b in spec.blocks]
         self.head = LMHead(spec.head, rt)
+        n_steps = getattr(spec, "step_vectors", 0)
+        self.steps = StepVectors((n_steps, spec.embedding.hidden_size), rt) if n_steps else None
         for call in spec.order:
+            step = getattr(call, "step", None)
+            if step is not None and not 0 <= step < n_steps:
+                raise ValueError(f"run order names step vector {step}, model has {n_steps}")
             if not 0 <= call.block < len(self.blocks):
                 raise ValueError(f"run order names block {call.block}, model has {len(self.blocks)}")
 
@@ -42,6 +47,8 @@ class DecoderModel:
 
         walk("embedding", self.embedding)
         walk("head", self.head)
+        if self.steps is not None:
+            walk("steps", self.steps)
         for i, b in enumerate(self.blocks):
             walk(f"blocks.{i}", b)
         return owners
@@ -189,6 +196,11 @@ class DecoderModel:
                     rec.bind(roles)
                     rec_key, rec_bufs = key, (pending, out)
                 pending = out
+                continue
+            if getattr(call, "step", None) is not None:
+                # (a block that takes a step vector adds it with its first norm's sum)
+                pending = block.forward(residual, pending, ctx, view, call.writes_cache,
+                                        step=self.steps.row(call.step))
                 continue
             next_norm = None
             if fold and block.folds_next and i + 1 < len(order):

@@ -114,20 +114,22 @@ class PagedKVSpec(CacheSpec):
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None        # size of a value where it is not the keys' (None: head_dim)
     paged = True
     shareable = True
 
     def allocate(self, rt, page_size, num_pages, slots):
         shape = (num_pages, self.num_kv_heads, page_size, self.head_dim)
+        vshape = shape[:3] + (self.value_dim or self.head_dim,)
         return (torch.zeros(shape, dtype=rt.dtype, device=rt.device),
-                torch.zeros(shape, dtype=rt.dtype, device=rt.device))
+                torch.zeros(vshape, dtype=rt.dtype, device=rt.device))
 
     def view(self, storage, group):
         return KVCacheView(storage[0], storage[1], group.dev_table, group.page_size, group.window,
                            group.index)
 
     def bytes_per_page(self, page_size, element_size):
-        return 2 * self.num_kv_heads * page_size * self.head_dim * element_size
+        return self.num_kv_heads * page_size * (self.head_dim + (self.value_dim or self.head_dim)) * element_size
 
 
 @dataclass
@@ -176,6 +178,56 @@ class StateSpec(CacheSpec):
 
     def reset(self, storage, slot):
         storage[slot].zero_()
+
+
+@dataclass
+class CompositeView:
+    """The views of a composite cache's parts, in the order of the spec's parts."""
+
+    parts: Tuple[Any, ...]
+
+    def __getitem__(self, i):
+        return self.parts[i]
+
+
+@dataclass(frozen=True)
+class CompositeCacheSpec(CacheSpec):
+    """What a mixer made of several mixers keeps: each part's cache, under one cache id.  It is
+    paged if a part is (all paged parts then follow one release rule, the same ``window``), and a
+    request's slot row serves the parts with state.  The state is not a function of the tokens of
+    full pages alone, so such a cache is not shared through a prefix tree."""
+
+    parts: Tuple[CacheSpec, ...] = ()
+
+    def __post_init__(self):
+        windows = {p.window for p in self.parts if p.paged}
+        if len(windows) > 1:
+            raise ValueError(f"the paged parts of one cache must share a window, got {sorted(map(str, windows))}")
+
+    @property
+    def paged(self):
+        return any(p.paged for p in self.parts)
+
+    @property
+    def window(self):
+        return next((p.window for p in self.parts if p.paged), None)
+
+    @property
+    def shareable(self):
+        return bool(self.parts) and all(p.paged and p.shareable for p in self.parts)
+
+    def allocate(self, rt, page_size, num_pages, slots):
+        return tuple(p.allocate(rt, page_size, num_pages if p.paged else None, slots) for p in self.parts)
+
+    def view(self, storage, group):
+        return CompositeView(tuple(p.view(s, group if p.paged else None) for p, s in zip(self.parts, storage)))
+
+    def reset(self, storage, slot):
+        for p, s in zip(self.parts, storage):
+            p.reset(s, slot)
+
+    def bytes_per_page(self, page_size, element_size):
+        return sum(p.bytes_per_page(page_size, element_size) for p in self.parts if p.paged)
 
 
 # ---------------------------------------------------------------------- runtime

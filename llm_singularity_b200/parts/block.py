@@ -183,3 +183,43 @@ class PostNormBlock(Part):
         if self.side is not None:
             h = self.side.forward(residual, h, ctx)
         return StreamCopy(h)
+
+
+@register_block("sandwich_norm")
+class SandwichBlock(Part):
+    """``x += mult * post1(mixer(norm1(x))); x += mult * post2(ffn(norm2(x)))``: a norm in front of and
+    behind every sublayer.  The stream is 32-bit and updated in place.  The norm behind a sublayer,
+    the sum and the norm in front of the next sublayer are one kernel, so the block hands its last
+    sublayer's output on as a ``NormedDelta`` that the next block's first norm, or the head's, takes.
+    ``step``: a vector that joins the stream before the block's first norm (a pass through looped
+    layers begins here)."""
+
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        self.mixer_norm = NORMS.build(spec.mixer_norm, rt)
+        self.mixer = MIXERS.build(spec.mixer, rt)
+        self.mixer_post_norm = NORMS.build(spec.mixer_post_norm, rt)
+        self.ffn = FEED_FORWARDS.build(spec.ffn, rt) if spec.ffn is not None else None
+        self.ffn_norm = NORMS.build(spec.ffn_norm, rt) if spec.ffn is not None else None
+        self.ffn_post_norm = NORMS.build(spec.ffn_post_norm, rt) if spec.ffn is not None else None
+        for n in (self.mixer_post_norm, self.ffn_post_norm):
+            if n is not None and not hasattr(n, "pending"):
+                raise ValueError(f"a norm of kind '{n.spec.kind}' cannot stand behind a sublayer (no pending)")
+
+    def children(self) -> Dict[str, Part]:
+        c = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "mixer_post_norm": self.mixer_post_norm}
+        if self.ffn is not None:
+            c.update(ffn_norm=self.ffn_norm, ffn=self.ffn, ffn_post_norm=self.ffn_post_norm)
+        return c
+
+    def forward(self, residual: torch.Tensor, pending, ctx, cache, writes_cache: bool = True, step=None):
+        mult = self.spec.residual_mult
+        h = self.mixer_norm.add_norm(residual, pending, step) if step is not None \
+            else self.mixer_norm.add_norm(residual, pending)
+        y = self.mixer.forward(h, ctx, cache, writes_cache)
+        if self.ffn is None:
+            return self.mixer_post_norm.pending(y, mult)
+        h = self.ffn_norm.add_norm(residual, self.mixer_post_norm.pending(y, mult))
+        return self.ffn_post_norm.pending(self.ffn.forward(h, ctx), mult)

@@ -1,6 +1,6 @@
 """Token embedding and output head.
 
-Embedding: ``h0[t, :] = E[id_t, :]`` with no scale and no position term
+Embedding: ``h0[t, :] = E[id_t, :]`` (times the spec's ``scale``, 1 in the reference) with no position term
 (reference: kernels/src/embedding.cu:12-26, models/llama/llama_model.cpp:424-425);
 the rows are widened into the 32-bit residual stream.
 
@@ -39,8 +39,30 @@ class Embedding(Part):
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         out = self.rt.empty(token_ids.shape[0], self.spec.hidden_size, dtype=torch.float32)
-        self.rt.ops.embedding(self.weight, token_ids, out)
+        scale = float(getattr(self.spec, "scale", 1.0))
+        if scale != 1.0:
+            self.rt.ops.embedding(self.weight, token_ids, out, scale)
+        else:
+            self.rt.ops.embedding(self.weight, token_ids, out)
         return out
+
+
+class StepVectors(Part):
+    """A table of vectors of model width, one of which the run order may add to the stream before
+    a layer call (the number of the pass through a looped stretch of layers).  32-bit."""
+
+    graph_safe = True
+
+    @classmethod
+    def params(cls, spec) -> Dict[str, ParamSpec]:
+        rows, width = spec
+        return {"table": ParamSpec((rows, width), role="vector", init="normal")}
+
+    def load(self, tensors):
+        self.table = tensors["table"].contiguous()
+
+    def row(self, i: int) -> torch.Tensor:
+        return self.table[i]
 
 
 class LMHead(Part):

@@ -1,0 +1,105 @@
+"""Softmax attention over a paged cache whose keys and values have sizes of their own.
+
+Per layer call: one product against the row-wise concatenation ``[Wq; Wk; Wv; Wg]`` -> one kernel
+that adds the biases, norms every head of q and k (RMS over the head, one weight of head size for
+all heads), applies the query temperature and the rotation, and writes queries to a buffer and
+keys and values to this step's cache places -> every query row attends the cached keys not after
+it, within its window and its chunk, query head ``h`` reading kv head ``h // (heads / kv_heads)``
+-> the heads' outputs times ``sigmoid(Wg x)`` -> output projection.  Each of bias, norm,
+temperature, rotation, window, chunk and gate is there only if the spec asks for it.  Scores,
+softmax, norms, positions and angles are 32-bit.
+
+Where the spec is what the framework's grouped attention already covers after the preparation (keys
+and values of one size, no chunks, no gate), the same attention kernels run (tensor cores for
+bfloat16 heads of 64 or 128); everything else runs the kernels of ``csrc/attention_dv.cu``.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .base import POSITIONS, PagedKVSpec, ParamSpec, Part, register_mixer
+
+
+@register_mixer("kv_attention")
+class KVAttention(Part):
+    graph_safe = True
+    kernels = ("gemm", "attention_prep", "attention_dv")
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        s = spec
+        if s.num_kv_heads <= 0 or s.num_heads % s.num_kv_heads:
+            raise ValueError(f"num_heads {s.num_heads} is not a multiple of num_kv_heads {s.num_kv_heads}")
+        for name, v in (("window", s.window), ("chunk", s.chunk)):
+            if v is not None and v < 1:
+                raise ValueError(f"{name} must be at least 1, got {v}")
+        if s.temp_every < 0:
+            raise ValueError(f"temp_every must not be negative, got {s.temp_every}")
+        self.position = POSITIONS.build(s.position, rt)
+        self.table = self.position.rotary_table()
+        if self.table is None and s.position.kind != "none":
+            raise ValueError(f"a position encoding of kind '{s.position.kind}' is not a rotation this mixer can fuse")
+        self.pairing = getattr(s.position, "pairing", "half")
+        self.q_size = s.num_heads * s.key_dim
+        self.k_size = s.num_kv_heads * s.key_dim
+        self.v_size = s.num_kv_heads * s.value_dim
+        self.o_size = s.num_heads * s.value_dim
+        # the framework's grouped attention takes over where nothing here is beyond it
+        self.plain = (s.key_dim == s.value_dim and s.chunk is None and not s.out_gate and s.key_dim % 16 == 0
+                      and 16 <= s.key_dim <= 256)
+        if self.plain:
+            self.kernels = self.kernels + ("attention",)
+            if rt.dtype == torch.bfloat16 and s.key_dim in (64, 128):
+                self.kernels = self.kernels + ("attention_tc", "attention_tc5")
+
+    @classmethod
+    def params(cls, spec) -> Dict[str, ParamSpec]:
+        s, H = spec, spec.hidden_size
+        q, k, v, o = s.num_heads * s.key_dim, s.num_kv_heads * s.key_dim, s.num_kv_heads * s.value_dim, \
+            s.num_heads * s.value_dim
+        p = {"q": ParamSpec((q, H)), "k": ParamSpec((k, H)), "v": ParamSpec((v, H)), "o": ParamSpec((H, o))}
+        if s.qkv_bias:
+            p.update(q_bias=ParamSpec((q,), role="vector", init="normal"),
+                     k_bias=ParamSpec((k,), role="vector", init="normal"),
+                     v_bias=ParamSpec((v,), role="vector", init="normal"))
+        if s.qk_norm:
+            p.update(q_norm=ParamSpec((s.key_dim,), role="vector", init="ones"),
+                     k_norm=ParamSpec((s.key_dim,), role="vector", init="ones"))
+        if s.out_gate:
+            p["g"] = ParamSpec((o, H))
+        return p
+
+    def children(self):
+        return {"position": self.position}
+
+    def load(self, tensors):
+        rows = [tensors["q"], tensors["k"], tensors["v"]] + ([tensors["g"]] if self.spec.out_gate else [])
+        self.w_in = torch.cat(rows, dim=0).contiguous()
+        self.w_out = tensors["o"].contiguous()
+        self.extras = {n: tensors[n].contiguous() for n in ("q_bias", "k_bias", "v_bias", "q_norm", "k_norm")
+                       if n in tensors}
+
+    def cache_spec(self):
+        s = self.spec
+        return PagedKVSpec(s.num_kv_heads, s.key_dim, s.window, None if s.value_dim == s.key_dim else s.value_dim)
+
+    def forward(self, x, ctx, cache, writes_cache: bool = True):
+        s, ops = self.spec, self.rt.ops
+        T = x.shape[0]
+        proj = ops.linear(x, self.w_in)                                   # [T, q | k | v | g]
+        q = self.rt.empty(T, self.q_size)
+        inv_freq, rotary_dim = self.table if self.table is not None else (None, 0)
+        ops.attention_prep(proj, 0, self.q_size, self.q_size + self.k_size, s.num_heads, s.num_kv_heads,
+                           s.key_dim, s.value_dim, ctx, cache, q, norm_eps=s.eps, temp_coef=s.temp_coef,
+                           temp_every=s.temp_every, inv_freq=inv_freq, rotary_dim=rotary_dim, pairing=self.pairing,
+                           store=writes_cache, **self.extras)
+        out = self.rt.empty(T, self.o_size)
+        if self.plain:
+            ops.paged_attention(q, s.num_heads, s.num_kv_heads, s.key_dim, ctx, cache, s.scale, s.window or 0, out)
+        else:
+            gate = proj[:, self.q_size + self.k_size + self.v_size:] if s.out_gate else None
+            ops.attention_dv(q, s.num_heads, s.num_kv_heads, s.key_dim, s.value_dim, ctx, cache, s.scale,
+                             s.window or 0, s.chunk or 0, gate, out)
+        return ops.linear(out, self.w_out)

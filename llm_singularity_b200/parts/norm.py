@@ -15,31 +15,80 @@ import torch
 from .base import ParamSpec, Part, register_norm
 
 
+class NormedDelta:
+    """A sublayer's output that a norm behind the sublayer still has to take before it joins the
+    stream: ``stream += mult * unit(values) * weight``.  Handed on in place of a plain delta, so
+    that this norm, the sum and the norm in front of the next sublayer are one kernel."""
+
+    __slots__ = ("values", "weight", "eps", "mult")
+
+    def __init__(self, values: torch.Tensor, weight: torch.Tensor, eps: float, mult: float):
+        self.values, self.weight, self.eps, self.mult = values, weight, float(eps), float(mult)
+
+
 @register_norm("rmsnorm")
 class RMSNorm(Part):
+    """``unit_offset`` in the spec: the checkpoint stores the weight's distance from one; one is added
+    (in 32-bit) when the weight is loaded, and the kernels see an ordinary weight."""
+
     graph_safe = True
     replayable = True
     foldable = True
     kernels = ("norm",)
 
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        if getattr(spec, "unit_offset", False):
+            self.kernels = self.kernels + ("sandwich",)
+
     @classmethod
     def params(cls, spec) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((spec.size,), role="vector", init="ones")}
+        init = "normal" if getattr(spec, "unit_offset", False) else "ones"
+        return {"weight": ParamSpec((spec.size,), role="vector", init=init)}
 
     def load(self, tensors):
         self.weight = tensors["weight"]
+        if getattr(self.spec, "unit_offset", False):
+            self.weight = (self.weight.float() + 1.0).contiguous()
+
+    def pending(self, values: torch.Tensor, mult: float = 1.0) -> NormedDelta:
+        """``values`` as something this norm takes before it is added to the stream ``mult`` times."""
+        return NormedDelta(values, self.weight, self.spec.eps, mult)
+
+    def _stream(self, residual, delta, step, rows):
+        """The sum and this norm through the kernel that also takes a norm behind the sublayer and a
+        step vector."""
+        y = w = None
+        eps, mult = 0.0, 1.0
+        if isinstance(delta, NormedDelta):
+            y, w, eps, mult = delta.values, delta.weight, delta.eps, delta.mult
+        elif isinstance(delta, torch.Tensor):
+            y = delta
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        out = self.rt.empty(n, residual.shape[1])
+        self.rt.ops.stream_norm(residual, y, w, eps, mult, step, rows, self.weight, self.spec.eps, out)
+        return out
 
     def fold(self):
         """What a product needs to take this norm upon itself: the weight and eps."""
         return self.weight, self.spec.eps
 
-    def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+    def add_norm(self, residual: torch.Tensor, delta, step: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``delta``: a tensor, None, a ``NormedDelta`` or a ``StreamCopy`` (nothing pending).  ``step``: a
+        vector added to every row of the stream with the sum."""
+        if isinstance(delta, StreamCopy):
+            delta = None
+        if isinstance(delta, NormedDelta) or step is not None:
+            return self._stream(residual, delta, step, None)
         out = self.rt.empty(*residual.shape)
         self.rt.ops.add_rmsnorm(residual, delta, self.weight, self.spec.eps, out)
         return out
 
-    def gather_add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor],
-                        rows: torch.Tensor) -> torch.Tensor:
+    def gather_add_norm(self, residual: torch.Tensor, delta, rows: torch.Tensor) -> torch.Tensor:
+        if isinstance(delta, StreamCopy):
+            delta = None
+        if isinstance(delta, NormedDelta):
+            return self._stream(residual, delta, None, rows)
         out = self.rt.empty(rows.shape[0], residual.shape[1])
         self.rt.ops.gather_add_rmsnorm(residual, delta, rows, self.weight, self.spec.eps, out)
         return out

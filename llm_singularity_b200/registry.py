@@ -77,6 +77,8 @@ def _register_builtin() -> None:
     register_architecture(LlamaConfig.architecture, LlamaConfig)
     from .config.ridotar import RidotarConfig
     register_architecture(RidotarConfig.architecture, RidotarConfig)
+    from .config.fogezen import FogezenConfig
+    register_architecture(FogezenConfig.architecture, FogezenConfig)
 
 
 _register_builtin()
