@@ -338,7 +338,7 @@ def run_design(args):
     sampler.start()
     rows = designs.compare(sizes=tuple(args.sizes.split(",")), batch=args.batch, context=min(args.context, 2048),
                            steps=min(args.steps, 32), warmup=max(args.warmup, 3),
-                           layers=args.layers if args.layers != FULL_LAYERS else None)
+                           layers=args.layers if args.layers != FULL_LAYERS else None, design=args.design)
     clocks = sampler.stop()
     print(json.dumps({"metric": f"{args.design} beside llama at equal size: prefill and decode tok/s",
                       "design": args.design, "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
@@ -359,7 +359,7 @@ def main():
     ap.add_argument("--windows", type=int, default=5, help="timed windows of K steps; the median is reported")
     ap.add_argument("--no-more", action="store_true", help="leave out the 3B and 8B serving runs")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--design", default=None, choices=["ridotar"],
+    ap.add_argument("--design", default=None, choices=["ridotar", "fogezen"],
                     help="instead of the headline: prefill and decode throughput of this design beside the "
                          "Llama decoder at equal size (llm_singularity_b200/measure/designs.py)")
     ap.add_argument("--sizes", default="w1024,w2048", help="with --design: sizes to run, comma-separated")

@@ -12,6 +12,17 @@
 //
 // Generic form (any sizes, 32-bit or bfloat16 storage): one warp owns a (row, head); lanes split
 // the keys of a 32-key stretch for the scores and the value dims for the weighted sum.
+//
+// Tensor-core form (bfloat16, dk and dv multiples of 16 up to 128): a block owns a request, a kv
+// head and 64 "rows", a row being (query position, query head of the kv head's group) with the
+// head running fastest, so that all heads of a group share every key and value tile that is
+// loaded.  Tiles of 64 keys and their values come from the pages into shared memory through
+// cp.async, two buffers deep; a warp holds 16 rows' queries as mma.sync A fragments, forms S = Q K^T
+// on the tensor cores (m16n8k16, 32-bit accumulators), does the masked softmax with a running
+// maximum in registers, and feeds the weights straight back as the A fragments of O += P V.  A
+// request that brings at most 16 rows (a single token: one row per head of the group) is handled by
+// the four warps side by side, each taking 16 of a tile's 64 keys, and merged through shared
+// memory at the end.
 #include "common.cuh"
 
 #include <float.h>
@@ -127,6 +138,324 @@ attention_dv_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_pag
             o[d] = lsb_from_float<T>(y);
         }
     }
+}
+
+// ------------------------------------------------------------------ tensor-core form
+constexpr int kMmaRows = 64, kMmaKeys = 64, kMmaThreads = 128;
+
+__device__ __forceinline__ void dv_mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void dv_cp_async16(void* dst, const void* src, bool real) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = real ? 16 : 0;                       // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ uint32_t dv_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int DKP, int DVP>
+__global__ void __launch_bounds__(kMmaThreads)
+attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
+                        const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ q_start,
+                        const int* __restrict__ kv_len_arr, const int* __restrict__ table_rows,
+                        const int* __restrict__ block_table, int table_stride,
+                        const __nv_bfloat16* __restrict__ gate, long long gate_stride,
+                        __nv_bfloat16* __restrict__ out, int nh, int nkv, int dk, int dv, int page_size,
+                        int num_pages, float scale_log2, int window, int chunk) {
+    constexpr int KS = DKP + 8, VS = DVP + 8;          // row strides in elements: 4 words past a multiple of 32
+    extern __shared__ __align__(16) unsigned char dv_smem[];
+    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(dv_smem);       // [2][64][KS]
+    __nv_bfloat16* Vs = Ks + 2 * kMmaKeys * KS;                          // [2][64][VS]
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int r = blockIdx.z, g = blockIdx.y, group = nh / nkv;
+    const int qs = q_start[r];
+    const int q_len = q_start[r + 1] - qs;
+    const int rows_total = q_len * group;
+    const int tile_row0 = blockIdx.x * kMmaRows;
+    if (tile_row0 >= rows_total) return;
+    const bool split = rows_total <= 16;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tid4 = lane & 3;
+    const int kv_len = kv_len_arr[r];
+    const int p_base = kv_len - q_len;
+    auto lowest = [&](int p) {
+        int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+        if (chunk > 0) lo = max(lo, (p / chunk) * chunk);
+        return lo;
+    };
+    const int last_row = min(tile_row0 + kMmaRows, rows_total) - 1;
+    const int last_pos = p_base + last_row / group;
+    const int kt0 = lowest(p_base + tile_row0 / group) / kMmaKeys, kt1 = last_pos / kMmaKeys;
+    const int* bt = block_table + (size_t)table_rows[r] * table_stride;
+
+    // this thread's two rows (gid and gid + 8 of the warp's slab)
+    const int slab = tile_row0 + (split ? 0 : warp * 16);
+    const int row_a = slab + gid, row_b = row_a + 8;
+    const bool ok_a = row_a < rows_total, ok_b = row_b < rows_total;
+    const int pos_a = p_base + row_a / group, pos_b = p_base + row_b / group;
+    const int lo_a = lowest(pos_a), lo_b = lowest(pos_b);
+    const int h_a = g * group + row_a % group, h_b = g * group + row_b % group;
+    const size_t t_a = (size_t)qs + row_a / group, t_b = (size_t)qs + row_b / group;
+    const int dk_steps = dk >> 4, dv_blocks = dv >> 3;
+
+    uint32_t qa[DKP / 16][4];
+    {
+        const __nv_bfloat16* qa_row = q + (t_a * nh + h_a) * dk;
+        const __nv_bfloat16* qb_row = q + (t_b * nh + h_b) * dk;
+#pragma unroll
+        for (int ks = 0; ks < DKP / 16; ++ks) {
+            qa[ks][0] = qa[ks][1] = qa[ks][2] = qa[ks][3] = 0u;
+            if (ks < dk_steps) {
+                const int c = ks * 16 + 2 * tid4;
+                if (ok_a) {
+                    qa[ks][0] = *reinterpret_cast<const uint32_t*>(qa_row + c);
+                    qa[ks][2] = *reinterpret_cast<const uint32_t*>(qa_row + c + 8);
+                }
+                if (ok_b) {
+                    qa[ks][1] = *reinterpret_cast<const uint32_t*>(qb_row + c);
+                    qa[ks][3] = *reinterpret_cast<const uint32_t*>(qb_row + c + 8);
+                }
+            }
+        }
+    }
+    float o[DVP / 8][4];
+#pragma unroll
+    for (int nb = 0; nb < DVP / 8; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f;
+    float m_a = -FLT_MAX, m_b = -FLT_MAX, l_a = 0.f, l_b = 0.f;
+
+    auto load_tile = [&](int kt, int buf) {
+        __nv_bfloat16* kd = Ks + buf * kMmaKeys * KS;
+        __nv_bfloat16* vd = Vs + buf * kMmaKeys * VS;
+        const int kper = dk >> 3, vper = dv >> 3, per = kper + vper;
+        for (int idx = threadIdx.x; idx < kMmaKeys * per; idx += kMmaThreads) {
+            const int n = idx / per, c = idx - n * per;
+            const int kj = kt * kMmaKeys + n;
+            long long at = -1;
+            if (kj <= last_pos) {
+                const int page = bt[kj / page_size];
+                if (page < 0 || page >= num_pages) lsb_set_status(LSB_BAD_PAGE);
+                else at = ((long long)page * nkv + g) * page_size + (kj % page_size);
+            }
+            if (c < kper) dv_cp_async16(kd + n * KS + c * 8, k_pages + (at < 0 ? 0 : at * dk + c * 8), at >= 0);
+            else dv_cp_async16(vd + n * VS + (c - kper) * 8, v_pages + (at < 0 ? 0 : at * dv + (c - kper) * 8), at >= 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    const bool active = split || slab < rows_total;    // a warp whose slab lies past the rows only helps loading
+    load_tile(kt0, 0);
+    for (int kt = kt0; kt <= kt1; ++kt) {
+        const int buf = (kt - kt0) & 1;
+        if (kt < kt1) {
+            load_tile(kt + 1, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        if (active) {
+            const __nv_bfloat16* kb = Ks + buf * kMmaKeys * KS;
+            const __nv_bfloat16* vb = Vs + buf * kMmaKeys * VS;
+            const int j_lo = split ? 2 * warp : 0, j_hi = split ? 2 * warp + 2 : 8;
+            float s[8][4];
+            float mx_a = -FLT_MAX, mx_b = -FLT_MAX;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+                if (j >= j_lo && j < j_hi) {
+                    const __nv_bfloat16* krow = kb + (j * 8 + gid) * KS + 2 * tid4;
+#pragma unroll
+                    for (int ks = 0; ks < DKP / 16; ++ks) {
+                        if (ks < dk_steps) {
+                            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 16);
+                            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8);
+                            dv_mma_16816(s[j], qa[ks], b0, b1);
+                        }
+                    }
+                    const int kj = kt * kMmaKeys + j * 8 + 2 * tid4;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = kj + (e & 1);
+                        const bool ok = e < 2 ? (ok_a && key >= lo_a && key <= pos_a) : (ok_b && key >= lo_b && key <= pos_b);
+                        s[j][e] = ok ? s[j][e] * scale_log2 : -FLT_MAX;
+                    }
+                    mx_a = fmaxf(mx_a, fmaxf(s[j][0], s[j][1]));
+                    mx_b = fmaxf(mx_b, fmaxf(s[j][2], s[j][3]));
+                }
+            }
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+            const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+            const float corr_a = exp2f(m_a - mn_a), corr_b = exp2f(m_b - mn_b);
+            m_a = mn_a;
+            m_b = mn_b;
+            float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (j >= j_lo && j < j_hi) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float pv = s[j][e] > -1e37f ? exp2f(s[j][e] - (e < 2 ? mn_a : mn_b)) : 0.f;
+                        s[j][e] = pv;
+                        if (e < 2) sum_a += pv;
+                        else sum_b += pv;
+                    }
+                }
+            }
+            l_a = l_a * corr_a + sum_a;
+            l_b = l_b * corr_b + sum_b;
+#pragma unroll
+            for (int nb = 0; nb < DVP / 8; ++nb) {
+                o[nb][0] *= corr_a;
+                o[nb][1] *= corr_a;
+                o[nb][2] *= corr_b;
+                o[nb][3] *= corr_b;
+            }
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                if (split ? kk == warp : true) {
+                    uint32_t pa[4];
+                    pa[0] = dv_pack(s[2 * kk][0], s[2 * kk][1]);
+                    pa[1] = dv_pack(s[2 * kk][2], s[2 * kk][3]);
+                    pa[2] = dv_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                    pa[3] = dv_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+                    const uint32_t vaddr = (uint32_t)__cvta_generic_to_shared(vb + (kk * 16 + (lane & 15)) * VS);
+#pragma unroll
+                    for (int nb = 0; nb < DVP / 8; ++nb) {
+                        if (nb < dv_blocks) {
+                            uint32_t b0, b1;
+                            asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                                         : "=r"(b0), "=r"(b1) : "r"(vaddr + nb * 16));
+                            dv_mma_16816(o[nb], pa, b0, b1);
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+
+    if (split) {
+        // every warp holds the same 16 rows over its own keys: merge through shared memory
+        float* part = reinterpret_cast<float*>(dv_smem);          // [4][16][DVP + 2]: O, then m and l
+        constexpr int PS = DVP + 2;
+        float* mine = part + (warp * 16) * PS;
+#pragma unroll
+        for (int nb = 0; nb < DVP / 8; ++nb) {
+            if (nb < dv_blocks) {
+                mine[gid * PS + nb * 8 + 2 * tid4] = o[nb][0];
+                mine[gid * PS + nb * 8 + 2 * tid4 + 1] = o[nb][1];
+                mine[(gid + 8) * PS + nb * 8 + 2 * tid4] = o[nb][2];
+                mine[(gid + 8) * PS + nb * 8 + 2 * tid4 + 1] = o[nb][3];
+            }
+        }
+        if (tid4 == 0) {
+            mine[gid * PS + DVP] = m_a;
+            mine[gid * PS + DVP + 1] = l_a;
+            mine[(gid + 8) * PS + DVP] = m_b;
+            mine[(gid + 8) * PS + DVP + 1] = l_b;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < rows_total * dv; idx += kMmaThreads) {
+            const int row = idx / dv, c = idx - row * dv;
+            float mm = -FLT_MAX;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) mm = fmaxf(mm, part[(w * 16 + row) * PS + DVP]);
+            float num = 0.f, den = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = exp2f(part[(w * 16 + row) * PS + DVP] - mm);
+                num += f * part[(w * 16 + row) * PS + c];
+                den += f * part[(w * 16 + row) * PS + DVP + 1];
+            }
+            float y = den > 0.f ? num / den : 0.f;
+            const size_t t = (size_t)qs + row / group;
+            const int h = g * group + row % group;
+            if (gate) y *= 1.f / (1.f + __expf(-__bfloat162float(gate[t * gate_stride + (size_t)h * dv + c])));
+            out[(t * nh + h) * dv + c] = __float2bfloat16_rn(y);
+        }
+        return;
+    }
+    if (!active) return;
+    const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
+#pragma unroll
+    for (int nb = 0; nb < DVP / 8; ++nb) {
+        if (nb < dv_blocks) {
+            const int c = nb * 8 + 2 * tid4;
+            if (ok_a) {
+                float y0 = o[nb][0] * inv_a, y1 = o[nb][1] * inv_a;
+                if (gate) {
+                    const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + t_a * gate_stride + (size_t)h_a * dv + c));
+                    y0 *= 1.f / (1.f + __expf(-gv.x));
+                    y1 *= 1.f / (1.f + __expf(-gv.y));
+                }
+                *reinterpret_cast<__nv_bfloat162*>(out + (t_a * nh + h_a) * dv + c) = __floats2bfloat162_rn(y0, y1);
+            }
+            if (ok_b) {
+                float y0 = o[nb][2] * inv_b, y1 = o[nb][3] * inv_b;
+                if (gate) {
+                    const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + t_b * gate_stride + (size_t)h_b * dv + c));
+                    y0 *= 1.f / (1.f + __expf(-gv.x));
+                    y1 *= 1.f / (1.f + __expf(-gv.y));
+                }
+                *reinterpret_cast<__nv_bfloat162*>(out + (t_b * nh + h_b) * dv + c) = __floats2bfloat162_rn(y0, y1);
+            }
+        }
+    }
+}
+
+// bfloat16 only; dk and dv multiples of 16, at most 128; q, the pages, the gate and out 16-byte aligned
+// with gate_stride even.
+LSB_API int lsb_attention_dv_mma_supported(int dk, int dv) {
+    return dk > 0 && dv > 0 && dk % 16 == 0 && dv % 16 == 0 && dk <= 128 && dv <= 128;
+}
+
+LSB_API int lsb_attention_dv_mma(const void* q, const void* k_pages, const void* v_pages, const int* q_start,
+                                 const int* kv_len, const int* table_rows, const int* block_table, int table_stride,
+                                 const void* gate, long long gate_stride, void* out, int n_requests, int max_q_len,
+                                 int nh, int nkv, int dk, int dv, int page_size, int num_pages, float scale, int window,
+                                 int chunk, cudaStream_t stream) {
+    if (n_requests <= 0 || max_q_len <= 0) return 0;
+    if (!lsb_attention_dv_mma_supported(dk, dv) || nkv <= 0 || nh % nkv || window < 0 || chunk < 0 || n_requests > 65535 ||
+        nkv > 65535 || (gate_stride & 1))
+        return (int)cudaErrorInvalidValue;
+    const int group = nh / nkv;
+    dim3 grid((max_q_len * group + kMmaRows - 1) / kMmaRows, nkv, n_requests);
+    const float scale_log2 = scale * 1.4426950408889634f;
+#define LSB_DV_MMA(DKP, DVP)                                                                                     \
+    do {                                                                                                         \
+        const size_t smem = (size_t)2 * kMmaKeys * ((DKP + 8) + (DVP + 8)) * sizeof(__nv_bfloat16);              \
+        if (smem > 48 * 1024) {                                                                                  \
+            int rc = (int)cudaFuncSetAttribute(attention_dv_mma_kernel<DKP, DVP>,                                \
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
+            if (rc) return rc;                                                                                   \
+        }                                                                                                        \
+        return lsb_launch(attention_dv_mma_kernel<DKP, DVP>, grid, dim3(kMmaThreads), smem, stream, 1,           \
+                          (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, \
+                          q_start, kv_len, table_rows, block_table, table_stride, (const __nv_bfloat16*)gate,    \
+                          gate_stride, (__nv_bfloat16*)out, nh, nkv, dk, dv, page_size, num_pages, scale_log2,   \
+                          window, chunk);                                                                        \
+    } while (0)
+    if (dk <= 64) {
+        if (dv <= 64) LSB_DV_MMA(64, 64);
+        else LSB_DV_MMA(64, 128);
+    } else {
+        if (dv <= 64) LSB_DV_MMA(128, 64);
+        else LSB_DV_MMA(128, 128);
+    }
+#undef LSB_DV_MMA
+    return 0;
 }
 
 LSB_API int lsb_attention_dv_max_dim() { return kDvMaxDim; }

@@ -1149,12 +1149,19 @@ def attention_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, nh: i
           _i(cache.k_pages.shape[0]), _i(1 if store else 0), _stream(proj))
 
 
+DV_TENSOR_CORES = True          # bfloat16 heads of multiples of 16 up to 128 on warp-level MMA (csrc/attention_dv.cu)
+
+
 def attention_dv(q: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, ctx, cache, scale: float, window: int,
                  chunk: int, gate: Optional[torch.Tensor], out: torch.Tensor) -> None:
     """Softmax attention of this step's queries ``q`` [T, nh * dk] over their requests' cached keys (size
     dk) and values (size dv): a query at position p sees ``[lo, p]`` with lo the larger of
     ``p - window + 1`` (window > 0) and the start of p's chunk of ``chunk`` positions (chunk > 0).
-    ``gate`` [T, nh * dv] (rows may be strided): out *= sigmoid(gate)."""
+    ``gate`` [T, nh * dv] (rows may be strided): out *= sigmoid(gate).
+
+    bfloat16 with both sizes multiples of 16 up to 128 runs on the tensor cores (prompt portions in
+    tiles of 64 rows, a row being a position and a head of a kv head's group; single tokens with the
+    keys of a tile dealt to four warps); everything else runs the generic kernel."""
     _req(q, "q", dim=2)
     _req(out, "out", q.dtype, 2)
     T = q.shape[0]
@@ -1171,6 +1178,14 @@ def attention_dv(q: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, ctx, cach
             raise KernelError("attention_dv: the gate must be [T, heads * value size] with unit column stride")
         gate_stride = gate.stride(0)
     _check_kv_cache(cache, nkv, dk, dv, q.dtype)
+    if (DV_TENSOR_CORES and q.dtype == torch.bfloat16 and gate_stride % 2 == 0
+            and (gate is None or gate.data_ptr() % 4 == 0)
+            and _lib("attention_dv").lsb_attention_dv_mma_supported(_i(dk), _i(dv))):
+        _call("attention_dv", "lsb_attention_dv_mma", _p(q), _p(cache.k_pages), _p(cache.v_pages), _p(ctx.q_start),
+              _p(ctx.kv_len), _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(gate),
+              _ll(gate_stride), _p(out), _i(ctx.n_requests), _i(ctx.max_q_len), _i(nh), _i(nkv), _i(dk), _i(dv),
+              _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale), _i(window), _i(chunk), _stream(out))
+        return
     _call("attention_dv", "lsb_attention_dv_generic", _p(q), _p(cache.k_pages), _p(cache.v_pages), _p(ctx.q_start),
           _p(ctx.kv_len), _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(gate),
           _ll(gate_stride), _p(out), _i(_dt(q)), _i(ctx.n_requests), _i(ctx.max_q_len), _i(nh), _i(nkv), _i(dk),

@@ -1,4 +1,9 @@
-"""Prefill and decode throughput of the Ridotar design beside the Llama decoder at equal size.
+"""Prefill and decode throughput of a design (Ridotar, Fogezen) beside the Llama decoder at equal size.
+
+Fogezen: layers alternating between biased attention with a query temperature and the parallel
+pair (chunked, gated attention with normed and rotated heads beside a matrix memory), the second
+layer run twice in a row as a loop (as many layer runs as the Llama model has layers), dense
+feed-forwards of the Llama model's width.
 
 For each size a Ridotar model (layers cycling through its three mixers, the fourth reading the
 third's latent cache; routed experts whose active width equals the dense model's feed-forward)
@@ -43,6 +48,25 @@ def ridotar_config(width, layers, experts, top, ff, kv_rank, vocab) -> dict:
             out.append({"type": "latent_attention", "mlp": mlp, "mixer": dict(latent, kv_from=i - 1)})
     return {"architecture": "Ridotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 4},
             "postln_alpha": 1.5, "token_side": {"dim": 32}, "layers": out}
+
+
+def fogezen_config(width, layers, experts, top, ff, kv_rank, vocab) -> dict:
+    heads = width // 128
+    mlp = {"kind": "dense", "ff": top * ff}
+    attention = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "q_temp": {"coef": 0.1, "every": 512}}
+    pair = {"left": {"heads": max(1, heads // 2), "kv_heads": max(1, heads // 8), "dim": 128, "vdim": 64,
+                     "scale": 128 ** -0.5, "mask": {"size": 1024}, "rot": {"base": 10000.0, "dims": 64}},
+            "right": {"heads": max(1, heads // 2), "dim": 64, "vdim": 128, "gate_cap": 15.0}}
+    stored = max(2, layers - 1)                   # one layer is run twice
+    out = [{"type": "parallel" if i % 2 else "attention", "mlp": mlp,
+            "mixer": dict(pair) if i % 2 else dict(attention)} for i in range(stored)]
+    return {"architecture": "Fogezen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"scale": float(width) ** 0.5}, "residual_mult": 0.5, "layers": out,
+            "loop": {"start": 1, "stop": 2, "times": 2 if layers > 2 else 1}}
+
+
+DESIGNS = {"ridotar": ridotar_config, "fogezen": fogezen_config}
 
 
 def llama_config(width, layers, experts, top, ff, kv_rank, vocab) -> dict:
@@ -119,7 +143,7 @@ def _measure(cfg_dict, vocab, prefill_tokens, batch, context, steps, warmup, rep
 
 
 def compare(sizes=("w1024", "w2048"), prefill_tokens=2048, batch=8, context=2048, steps=32, warmup=8, reps=5,
-            layers=None) -> Dict[str, dict]:
+            layers=None, design="ridotar") -> Dict[str, dict]:
     import gc
     out = {}
     for name in sizes:
@@ -127,11 +151,11 @@ def compare(sizes=("w1024", "w2048"), prefill_tokens=2048, batch=8, context=2048
         if layers:
             size["layers"] = layers
         row = {"size": size}
-        for design, make in (("ridotar", ridotar_config), ("llama", llama_config)):
-            row[design] = _measure(make(**size), size["vocab"], prefill_tokens, batch, context, steps, warmup, reps)
+        for which, make in ((design, DESIGNS[design]), ("llama", llama_config)):
+            row[which] = _measure(make(**size), size["vocab"], prefill_tokens, batch, context, steps, warmup, reps)
             gc.collect()
             torch.cuda.empty_cache()
-        row["ridotar_over_llama"] = {"prefill": round(row["ridotar"]["prefill_tok_s"] / row["llama"]["prefill_tok_s"], 3),
-                                     "decode": round(row["ridotar"]["decode_tok_s"] / row["llama"]["decode_tok_s"], 3)}
+        row[design + "_over_llama"] = {"prefill": round(row[design]["prefill_tok_s"] / row["llama"]["prefill_tok_s"], 3),
+                                       "decode": round(row[design]["decode_tok_s"] / row["llama"]["decode_tok_s"], 3)}
         out[name] = row
     return out
