@@ -228,31 +228,41 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     for (int nb = 0; nb < DVP / 8; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f;
     float m_a = -FLT_MAX, m_b = -FLT_MAX, l_a = 0.f, l_b = 0.f;
 
-    auto load_tile = [&](int kt, int buf) {
-        __nv_bfloat16* kd = Ks + buf * kMmaKeys * KS;
-        __nv_bfloat16* vd = Vs + buf * kMmaKeys * VS;
-        const int kper = dk >> 3, vper = dv >> 3, per = kper + vper;
-        for (int idx = threadIdx.x; idx < kMmaKeys * per; idx += kMmaThreads) {
-            const int n = idx / per, c = idx - n * per;
-            const int kj = kt * kMmaKeys + n;
-            long long at = -1;
-            if (kj <= last_pos) {
-                const int page = bt[kj / page_size];
-                if (page < 0 || page >= num_pages) lsb_set_status(LSB_BAD_PAGE);
-                else at = ((long long)page * nkv + g) * page_size + (kj % page_size);
-            }
-            if (c < kper) dv_cp_async16(kd + n * KS + c * 8, k_pages + (at < 0 ? 0 : at * dk + c * 8), at >= 0);
-            else dv_cp_async16(vd + n * VS + (c - kper) * 8, v_pages + (at < 0 ? 0 : at * dv + (c - kper) * 8), at >= 0);
+    // Loading: a thread owns half of one key row of a tile (its key chunks, then its value chunks, 16
+    // bytes each).  The row's place in the pages is looked up one tile ahead of the copies that need it,
+    // so that the block table's latency passes behind the tile being worked on.
+    const int my_row = threadIdx.x >> 1, my_half = threadIdx.x & 1;
+    auto place = [&](int kt) -> long long {
+        const int kj = kt * kMmaKeys + my_row;
+        if (kt > kt1 || kj > last_pos) return -1;
+        const int page = bt[kj / page_size];
+        if (page < 0 || page >= num_pages) {
+            lsb_set_status(LSB_BAD_PAGE);
+            return -1;
         }
+        return ((long long)page * nkv + g) * page_size + (kj % page_size);
+    };
+    auto load_tile = [&](long long at, int buf) {
+        __nv_bfloat16* kd = Ks + (buf * kMmaKeys + my_row) * KS;
+        __nv_bfloat16* vd = Vs + (buf * kMmaKeys + my_row) * VS;
+        const __nv_bfloat16* ksrc = k_pages + (at < 0 ? 0 : at * dk);
+        const __nv_bfloat16* vsrc = v_pages + (at < 0 ? 0 : at * dv);
+        const int kper = dk >> 3, vper = dv >> 3;
+#pragma unroll 4
+        for (int c = my_half; c < kper; c += 2) dv_cp_async16(kd + c * 8, ksrc + (at < 0 ? 0 : c * 8), at >= 0);
+#pragma unroll 4
+        for (int c = my_half; c < vper; c += 2) dv_cp_async16(vd + c * 8, vsrc + (at < 0 ? 0 : c * 8), at >= 0);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
     const bool active = split || slab < rows_total;    // a warp whose slab lies past the rows only helps loading
-    load_tile(kt0, 0);
+    load_tile(place(kt0), 0);
+    long long at_next = place(kt0 + 1);
     for (int kt = kt0; kt <= kt1; ++kt) {
         const int buf = (kt - kt0) & 1;
         if (kt < kt1) {
-            load_tile(kt + 1, buf ^ 1);
+            load_tile(at_next, buf ^ 1);
+            at_next = place(kt + 2);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");

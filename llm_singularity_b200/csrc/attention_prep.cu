@@ -12,7 +12,8 @@
 //
 // Each of the first four is optional.  The projections come as rows of one matrix, q at q_off, k
 // at k_off, v at v_off, in the compute dtype.  One block per token, one warp per head at a time;
-// a head waits in shared memory between the norm and the rotation.
+// a head waits in shared memory between the norm and the rotation; a token's sines and cosines are
+// formed once and serve all its heads.
 #include "common.cuh"
 
 LSB_DEFINE_STATUS()
@@ -34,11 +35,18 @@ struct PrepArgs {
 template <typename T>
 __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArgs a) {
     __shared__ float head_sh[kPrepWarps][kPrepMaxDim];
+    __shared__ float cs_sh[2][kPrepMaxDim / 2];
     lsb_pdl_launch_dependents();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // positions are metadata of the step (on the device before its first kernel starts): the
+    // temperature and the token's sines and cosines, shared by all its heads, are formed while the
+    // projection before this kernel is still running
     const int pos = a.positions[t];
     float temp = 1.f;
     if (a.temp_every > 0) temp = 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every) + 1.f);
+    for (int i = threadIdx.x; i < (a.rotary_dim >> 1); i += blockDim.x)
+        sincosf((float)pos * a.inv_freq[i], &cs_sh[1][i], &cs_sh[0][i]);
+    __syncthreads();
     lsb_pdl_wait();                                 // (the block table is written by a kernel of this step)
     long long k_base = -1, v_base = -1;             // element offsets of (page, head 0, offset, 0)
     if (a.store) {
@@ -92,8 +100,7 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArg
                 float x0 = hs[ia] * (nw ? inv * nw[ia] : 1.f) * mul;
                 float x1 = ib < a.dk ? hs[ib] * (nw ? inv * nw[ib] : 1.f) * mul : 0.f;
                 if (i < half_rot) {
-                    float s, c;
-                    sincosf((float)pos * a.inv_freq[i], &s, &c);
+                    const float c = cs_sh[0][i], s = cs_sh[1][i];
                     const float r0 = x0 * c - x1 * s, r1 = x1 * c + x0 * s;
                     x0 = r0;
                     x1 = r1;

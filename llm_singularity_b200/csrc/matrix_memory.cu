@@ -13,24 +13,26 @@
 //     o = S^T q / (max(|n . q|, floor_t) + 1e-6)
 //     y = o / sqrt(mean(o^2) + eps) * w[head, :] * sigmoid(gate)         (mean over the head's values)
 //
-// The chain of maxima is walked in order by one lane per (request, head), with exactly the
-// arithmetic above, while the transcendental functions on either side of it are spread over the
-// warp.  Everything here is 32-bit.
+// The chain of maxima is walked in order, one warp per (request, head), with exactly the arithmetic
+// above, while the transcendental functions on either side of it are spread over the lanes.
+// Everything here is 32-bit.
 #include "common.cuh"
 
 LSB_DEFINE_STATUS()
 
-constexpr int kGateChunk = 128;       // tokens staged at a time (four per lane)
+constexpr int kGatePer = 4;           // tokens a lane holds of a stretch of 128
 
 __device__ __forceinline__ float mm_logsigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
 // raw [tokens, 2 * heads]: zi of every head, then zf.  gates [3][tokens][heads]: keep, write, floor.
-// m_state [slots, heads].
+// m_state [slots, heads].  One warp per (request, head): a lane holds four tokens of a stretch (token
+// c * 32 + lane), their gates are formed side by side, the chain of maxima then runs through all 128
+// in order on every lane alike (the values come by shuffle, which does not wait for the chain), and
+// the projections of the next stretch are on their way meanwhile.
 __global__ void __launch_bounds__(32)
 memory_gates_kernel(const float* __restrict__ raw, const float* __restrict__ i_bias, const float* __restrict__ f_bias,
                     float cap, float* __restrict__ m_state, int n_slots, const int* __restrict__ q_start,
                     const int* __restrict__ table_rows, float* __restrict__ gates, int tokens, int heads) {
-    __shared__ float i_sh[kGateChunk], f_sh[kGateChunk], m_sh[kGateChunk + 1];
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
     const int h = blockIdx.x, r = blockIdx.y, lane = threadIdx.x;
@@ -43,33 +45,53 @@ memory_gates_kernel(const float* __restrict__ raw, const float* __restrict__ i_b
     float m = m_state[(size_t)slot * heads + h];
     const float bi = i_bias ? i_bias[h] : 0.f, bf = f_bias ? f_bias[h] : 0.f;
     const size_t plane = (size_t)tokens * heads;
-    for (int base = t0; base < t1; base += kGateChunk) {
-        const int n = min(kGateChunk, t1 - base);
-        for (int j = lane; j < n; j += 32) {
-            const float* z = raw + (size_t)(base + j) * 2 * heads;
-            i_sh[j] = cap * tanhf((z[h] + bi) / cap);
-            f_sh[j] = mm_logsigmoid(cap * tanhf((z[heads + h] + bf) / cap));
+    float zi[kGatePer], zf[kGatePer];
+    auto fetch = [&](int base) {
+#pragma unroll
+        for (int c = 0; c < kGatePer; ++c) {
+            const int t = base + c * 32 + lane;
+            zi[c] = t < t1 ? raw[(size_t)t * 2 * heads + h] : 0.f;
+            zf[c] = t < t1 ? raw[(size_t)t * 2 * heads + heads + h] : 0.f;
         }
-        __syncwarp();
-        if (lane == 0) {
-            m_sh[0] = m;
-            float cur = m;
+    };
+    fetch(t0);
+    for (int base = t0; base < t1; base += 32 * kGatePer) {
+        float gi[kGatePer], gf[kGatePer], before[kGatePer], now[kGatePer];
+#pragma unroll
+        for (int c = 0; c < kGatePer; ++c) {
+            gi[c] = cap * tanhf((zi[c] + bi) / cap);
+            gf[c] = mm_logsigmoid(cap * tanhf((zf[c] + bf) / cap));
+            before[c] = now[c] = 0.f;
+        }
+        if (base + 32 * kGatePer < t1) fetch(base + 32 * kGatePer);
+#pragma unroll
+        for (int c = 0; c < kGatePer; ++c) {
+            const int left = t1 - (base + c * 32);              // tokens of this group of 32 (the same on every lane)
+            if (left <= 0) break;
 #pragma unroll 8
-            for (int j = 0; j < n; ++j) {
-                cur = fmaxf(f_sh[j] + cur, i_sh[j]);
-                m_sh[j + 1] = cur;
+            for (int l = 0; l < 32; ++l) {
+                const float fj = __shfl_sync(0xffffffffu, gf[c], l);
+                const float ij = __shfl_sync(0xffffffffu, gi[c], l);
+                if (l < left) {
+                    const float prev = m;
+                    m = fmaxf(fj + m, ij);
+                    if (l == lane) {
+                        before[c] = prev;
+                        now[c] = m;
+                    }
+                }
             }
         }
-        __syncwarp();
-        for (int j = lane; j < n; j += 32) {
-            const float before = m_sh[j], now = m_sh[j + 1];
-            const size_t at = (size_t)(base + j) * heads + h;
-            gates[at] = expf(f_sh[j] + before - now);
-            gates[plane + at] = expf(i_sh[j] - now);
-            gates[2 * plane + at] = expf(-now);
+#pragma unroll
+        for (int c = 0; c < kGatePer; ++c) {
+            const int t = base + c * 32 + lane;
+            if (t < t1) {
+                const size_t at = (size_t)t * heads + h;
+                gates[at] = expf(gf[c] + before[c] - now[c]);
+                gates[plane + at] = expf(gi[c] - now[c]);
+                gates[2 * plane + at] = expf(-now[c]);
+            }
         }
-        m = m_sh[n];
-        __syncwarp();
     }
     if (lane == 0) m_state[(size_t)slot * heads + h] = m;
 }
