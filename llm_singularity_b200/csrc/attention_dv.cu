@@ -19,10 +19,11 @@
 // loaded.  Tiles of 64 keys and their values come from the pages into shared memory through
 // cp.async, two buffers deep; a warp holds 16 rows' queries as mma.sync A fragments, forms S = Q K^T
 // on the tensor cores (m16n8k16, 32-bit accumulators), does the masked softmax with a running
-// maximum in registers, and feeds the weights straight back as the A fragments of O += P V.  A
-// request that brings at most 16 rows (a single token: one row per head of the group) is handled by
-// the four warps side by side, each taking 16 of a tile's 64 keys, and merged through shared
-// memory at the end.
+// maximum in registers, and feeds the weights straight back as the A fragments of O += P V.
+// Where 64-row blocks would leave most of the chip idle (single tokens: one row per head of the
+// group; one short prompt of a narrow model) a block owns 16 rows instead and its four warps work
+// side by side, each on 16 of a tile's 64 keys, merging through shared memory at the end; the ring
+// of tiles is then four deep where the blocks are few, since such a step waits on memory alone.
 #include "common.cuh"
 
 #include <float.h>
@@ -158,7 +159,7 @@ __device__ __forceinline__ uint32_t dv_pack(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int DKP, int DVP>
+template <int DKP, int DVP, int STAGES, bool NARROW>
 __global__ void __launch_bounds__(kMmaThreads)
 attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
                         const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ q_start,
@@ -166,20 +167,25 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int* __restrict__ block_table, int table_stride,
                         const __nv_bfloat16* __restrict__ gate, long long gate_stride,
                         __nv_bfloat16* __restrict__ out, int nh, int nkv, int dk, int dv, int page_size,
-                        int num_pages, float scale_log2, int window, int chunk) {
+                        int num_pages, float scale_log2, int window, int chunk, int ksplit, float* __restrict__ scratch) {
     constexpr int KS = DKP + 8, VS = DVP + 8;          // row strides in elements: 4 words past a multiple of 32
     extern __shared__ __align__(16) unsigned char dv_smem[];
-    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(dv_smem);       // [2][64][KS]
-    __nv_bfloat16* Vs = Ks + 2 * kMmaKeys * KS;                          // [2][64][VS]
+    __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(dv_smem);       // [STAGES][64][KS]
+    __nv_bfloat16* Vs = Ks + STAGES * kMmaKeys * KS;                     // [STAGES][64][VS]
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
     const int r = blockIdx.z, g = blockIdx.y, group = nh / nkv;
     const int qs = q_start[r];
     const int q_len = q_start[r + 1] - qs;
     const int rows_total = q_len * group;
-    const int tile_row0 = blockIdx.x * kMmaRows;
+    constexpr bool split = NARROW;                     // 16 rows a block, the warps side by side on the keys
+    constexpr int NJ = NARROW ? 2 : 8;                 // blocks of 8 keys a warp takes of a tile
+    constexpr int NKK = NARROW ? 1 : 4;                // and the same keys as k-steps of 16
+    const int block_rows = split ? 16 : kMmaRows;
+    // (16-row blocks may share a row tile's keys among `ksplit` blocks, merged by a second kernel)
+    const int row_tile = NARROW ? blockIdx.x / ksplit : blockIdx.x, key_part = NARROW ? blockIdx.x % ksplit : 0;
+    const int tile_row0 = row_tile * block_rows;
     if (tile_row0 >= rows_total) return;
-    const bool split = rows_total <= 16;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tid4 = lane & 3;
     const int kv_len = kv_len_arr[r];
     const int p_base = kv_len - q_len;
@@ -188,9 +194,14 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         if (chunk > 0) lo = max(lo, (p / chunk) * chunk);
         return lo;
     };
-    const int last_row = min(tile_row0 + kMmaRows, rows_total) - 1;
+    const int last_row = min(tile_row0 + block_rows, rows_total) - 1;
     const int last_pos = p_base + last_row / group;
-    const int kt0 = lowest(p_base + tile_row0 / group) / kMmaKeys, kt1 = last_pos / kMmaKeys;
+    int kt0 = lowest(p_base + tile_row0 / group) / kMmaKeys, kt1 = last_pos / kMmaKeys;
+    if (NARROW && ksplit > 1) {                       // this block's share of the key tiles (it may be empty)
+        const int per = (kt1 - kt0 + ksplit) / ksplit;
+        kt0 += key_part * per;
+        kt1 = min(kt1, kt0 + per - 1);
+    }
     const int* bt = block_table + (size_t)table_rows[r] * table_stride;
 
     // this thread's two rows (gid and gid + 8 of the warp's slab)
@@ -256,47 +267,72 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     };
 
     const bool active = split || slab < rows_total;    // a warp whose slab lies past the rows only helps loading
-    load_tile(place(kt0), 0);
-    long long at_next = place(kt0 + 1);
+    // the padding of the key and value rows (columns past dk and dv) is zeroed once; copies never touch it
+    for (int idx = threadIdx.x; idx < STAGES * kMmaKeys; idx += kMmaThreads) {
+        for (int c = dk; c < DKP; ++c) Ks[idx * KS + c] = __float2bfloat16_rn(0.f);
+        for (int c = dv; c < DVP; ++c) Vs[idx * VS + c] = __float2bfloat16_rn(0.f);
+    }
+    // a group of copies is committed for every tile slot, real or not, so that the count the wait
+    // names is the same in every round
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) {
+        if (kt0 + st <= kt1) load_tile(place(kt0 + st), st);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    long long at_next = place(kt0 + STAGES - 1);
+    // rows of this warp see every key of a tile that lies wholly between these two
+    const int slab_lo = lowest(p_base + min(slab + 15, rows_total - 1) / group), slab_hi = p_base + slab / group;
+    const bool slab_full = slab + 15 < rows_total;
     for (int kt = kt0; kt <= kt1; ++kt) {
-        const int buf = (kt - kt0) & 1;
-        if (kt < kt1) {
-            load_tile(at_next, buf ^ 1);
-            at_next = place(kt + 2);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
+        const int buf = (kt - kt0) % STAGES;
+        if (kt + STAGES - 1 <= kt1) load_tile(at_next, (kt - kt0 + STAGES - 1) % STAGES);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        at_next = place(kt + STAGES);
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");
         __syncthreads();
         if (active) {
-            const __nv_bfloat16* kb = Ks + buf * kMmaKeys * KS;
-            const __nv_bfloat16* vb = Vs + buf * kMmaKeys * VS;
-            const int j_lo = split ? 2 * warp : 0, j_hi = split ? 2 * warp + 2 : 8;
-            float s[8][4];
-            float mx_a = -FLT_MAX, mx_b = -FLT_MAX;
+            // (nothing in the blocks of tensor-core work below depends on a run-time size: the padding
+            // of K and of the queries is zero, and the columns of O past dv are never written out, so
+            // the compiler is free to keep many independent MMAs in flight)
+            const int key0 = NARROW ? warp * 16 : 0;           // this warp's first key of the tile
+            const __nv_bfloat16* kb = Ks + (buf * kMmaKeys + key0) * KS;
+            const __nv_bfloat16* vb = Vs + (buf * kMmaKeys + key0) * VS;
+            float s[NJ][4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-                if (j >= j_lo && j < j_hi) {
-                    const __nv_bfloat16* krow = kb + (j * 8 + gid) * KS + 2 * tid4;
+            for (int j = 0; j < NJ; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
 #pragma unroll
-                    for (int ks = 0; ks < DKP / 16; ++ks) {
-                        if (ks < dk_steps) {
-                            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks * 16);
-                            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8);
-                            dv_mma_16816(s[j], qa[ks], b0, b1);
-                        }
-                    }
-                    const int kj = kt * kMmaKeys + j * 8 + 2 * tid4;
+            for (int ks = 0; ks < DKP / 16; ++ks) {
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) {
+                    const __nv_bfloat16* krow = kb + (j * 8 + gid) * KS + 2 * tid4 + ks * 16;
+                    dv_mma_16816(s[j], qa[ks], *reinterpret_cast<const uint32_t*>(krow),
+                                 *reinterpret_cast<const uint32_t*>(krow + 8));
+                }
+            }
+            const int tile_key0 = kt * kMmaKeys + key0;
+            const bool interior = slab_full && tile_key0 >= slab_lo && tile_key0 + NJ * 8 - 1 <= slab_hi;
+            if (interior) {
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[j][e] *= scale_log2;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const int key = kj + (e & 1);
+                        const int key = tile_key0 + j * 8 + 2 * tid4 + (e & 1);
                         const bool ok = e < 2 ? (ok_a && key >= lo_a && key <= pos_a) : (ok_b && key >= lo_b && key <= pos_b);
                         s[j][e] = ok ? s[j][e] * scale_log2 : -FLT_MAX;
                     }
-                    mx_a = fmaxf(mx_a, fmaxf(s[j][0], s[j][1]));
-                    mx_b = fmaxf(mx_b, fmaxf(s[j][2], s[j][3]));
                 }
+            }
+            float mx_a = -FLT_MAX, mx_b = -FLT_MAX;
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                mx_a = fmaxf(mx_a, fmaxf(s[j][0], s[j][1]));
+                mx_b = fmaxf(mx_b, fmaxf(s[j][2], s[j][3]));
             }
             mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
             mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
@@ -308,15 +344,14 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             m_b = mn_b;
             float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                if (j >= j_lo && j < j_hi) {
+            for (int j = 0; j < NJ; ++j) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float pv = s[j][e] > -1e37f ? exp2f(s[j][e] - (e < 2 ? mn_a : mn_b)) : 0.f;
-                        s[j][e] = pv;
-                        if (e < 2) sum_a += pv;
-                        else sum_b += pv;
-                    }
+                for (int e = 0; e < 4; ++e) {
+                    // (a masked score is -FLT_MAX; while a row has seen no key its maximum is that too)
+                    const float pv = s[j][e] > -1e37f ? exp2f(s[j][e] - (e < 2 ? mn_a : mn_b)) : 0.f;
+                    s[j][e] = pv;
+                    if (e < 2) sum_a += pv;
+                    else sum_b += pv;
                 }
             }
             l_a = l_a * corr_a + sum_a;
@@ -329,23 +364,19 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                 o[nb][3] *= corr_b;
             }
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-                if (split ? kk == warp : true) {
-                    uint32_t pa[4];
-                    pa[0] = dv_pack(s[2 * kk][0], s[2 * kk][1]);
-                    pa[1] = dv_pack(s[2 * kk][2], s[2 * kk][3]);
-                    pa[2] = dv_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-                    pa[3] = dv_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-                    const uint32_t vaddr = (uint32_t)__cvta_generic_to_shared(vb + (kk * 16 + (lane & 15)) * VS);
+            for (int kk = 0; kk < NKK; ++kk) {
+                uint32_t pa[4];
+                pa[0] = dv_pack(s[2 * kk][0], s[2 * kk][1]);
+                pa[1] = dv_pack(s[2 * kk][2], s[2 * kk][3]);
+                pa[2] = dv_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pa[3] = dv_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+                const uint32_t vaddr = (uint32_t)__cvta_generic_to_shared(vb + (kk * 16 + (lane & 15)) * VS);
 #pragma unroll
-                    for (int nb = 0; nb < DVP / 8; ++nb) {
-                        if (nb < dv_blocks) {
-                            uint32_t b0, b1;
-                            asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
-                                         : "=r"(b0), "=r"(b1) : "r"(vaddr + nb * 16));
-                            dv_mma_16816(o[nb], pa, b0, b1);
-                        }
-                    }
+                for (int nb = 0; nb < DVP / 8; ++nb) {
+                    uint32_t b0, b1;
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                                 : "=r"(b0), "=r"(b1) : "r"(vaddr + nb * 16));
+                    dv_mma_16816(o[nb], pa, b0, b1);
                 }
             }
         }
@@ -377,17 +408,28 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             mine[(gid + 8) * PS + DVP + 1] = l_b;
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < rows_total * dv; idx += kMmaThreads) {
-            const int row = idx / dv, c = idx - row * dv;
+        const int rows_here = last_row - tile_row0 + 1;
+        for (int idx = threadIdx.x; idx < rows_here * dv; idx += kMmaThreads) {
+            const int row_l = idx / dv, c = idx - row_l * dv, row = tile_row0 + row_l;
             float mm = -FLT_MAX;
 #pragma unroll
-            for (int w = 0; w < 4; ++w) mm = fmaxf(mm, part[(w * 16 + row) * PS + DVP]);
+            for (int w = 0; w < 4; ++w) mm = fmaxf(mm, part[(w * 16 + row_l) * PS + DVP]);
             float num = 0.f, den = 0.f;
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-                const float f = exp2f(part[(w * 16 + row) * PS + DVP] - mm);
-                num += f * part[(w * 16 + row) * PS + c];
-                den += f * part[(w * 16 + row) * PS + DVP + 1];
+                const float f = exp2f(part[(w * 16 + row_l) * PS + DVP] - mm);
+                num += f * part[(w * 16 + row_l) * PS + c];
+                den += f * part[(w * 16 + row_l) * PS + DVP + 1];
+            }
+            if (ksplit > 1) {                          // sums relative to mm, then mm and the weights' sum
+                float* dst = scratch + ((((size_t)r * nkv + g) * (gridDim.x / ksplit) + row_tile) * ksplit + key_part) * 16 * (dv + 2) +
+                             (size_t)row_l * (dv + 2);
+                dst[c] = num;
+                if (c == 0) {
+                    dst[dv] = mm;
+                    dst[dv + 1] = den;
+                }
+                continue;
             }
             float y = den > 0.f ? num / den : 0.f;
             const size_t t = (size_t)qs + row / group;
@@ -425,7 +467,74 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     }
 }
 
-// bfloat16 only; dk and dv multiples of 16, at most 128; q, the pages, the gate and out 16-byte aligned
+// The partial sums of `ksplit` blocks that shared a row tile's keys, brought together:
+// scratch [request, kv head, row tile, part, 16 rows, dv + 2].
+constexpr int kMaxParts = 8;
+__global__ void __launch_bounds__(kMmaThreads)
+attention_dv_merge_kernel(const float* __restrict__ scratch, const int* __restrict__ q_start,
+                          const __nv_bfloat16* __restrict__ gate, long long gate_stride,
+                          __nv_bfloat16* __restrict__ out, int nh, int nkv, int dv, int ksplit) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int r = blockIdx.z, g = blockIdx.y, group = nh / nkv;
+    const int qs = q_start[r];
+    const int rows_total = (q_start[r + 1] - qs) * group;
+    const int tile_row0 = blockIdx.x * 16;
+    if (tile_row0 >= rows_total) return;
+    const int rows_here = min(16, rows_total - tile_row0);
+    const float* base = scratch + (((size_t)r * nkv + g) * gridDim.x + blockIdx.x) * ksplit * 16 * (dv + 2);
+    for (int idx = threadIdx.x; idx < rows_here * dv; idx += kMmaThreads) {
+        const int row_l = idx / dv, c = idx - row_l * dv, row = tile_row0 + row_l;
+        // (all parts' values are asked for at once: at most kMaxParts of them)
+        float pm[kMaxParts], pl[kMaxParts], pv[kMaxParts];
+#pragma unroll
+        for (int p = 0; p < kMaxParts; ++p) {
+            const float* src = base + ((size_t)(p < ksplit ? p : 0) * 16 + row_l) * (dv + 2);
+            pm[p] = p < ksplit ? src[dv] : -FLT_MAX;
+            pl[p] = p < ksplit ? src[dv + 1] : 0.f;
+            pv[p] = p < ksplit ? src[c] : 0.f;
+        }
+        float mm = -FLT_MAX;
+#pragma unroll
+        for (int p = 0; p < kMaxParts; ++p) mm = fmaxf(mm, pm[p]);
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int p = 0; p < kMaxParts; ++p) {
+            const float f = exp2f(pm[p] - mm);
+            num += f * pv[p];
+            den += f * pl[p];
+        }
+        float y = den > 0.f ? num / den : 0.f;
+        const size_t t = (size_t)qs + row / group;
+        const int h = g * group + row % group;
+        if (gate) y *= 1.f / (1.f + __expf(-__bfloat162float(gate[t * gate_stride + (size_t)h * dv + c])));
+        out[(t * nh + h) * dv + c] = __float2bfloat16_rn(y);
+    }
+}
+
+// How a step of this shape is launched: bit 0: 16-row blocks; bit 1: four tiles in flight; bits 8..:
+// how many blocks share a row tile's keys.  A function of the shape alone (never of the sequences'
+// lengths), so that a captured launch stays valid as sequences grow.  shape: 0 chooses; 1: 64-row
+// blocks; 2: 16-row blocks, two tiles in flight; 3: 16-row blocks, four; 4: as 3, keys shared by 3 blocks.
+LSB_API int lsb_attention_dv_mma_plan(int n_requests, int max_q_len, int nh, int nkv, int chunk, int sms, int shape) {
+    if (sms <= 0) sms = 148;
+    const long long rows = (long long)max_q_len * (nh / nkv);
+    const long long wide = (rows + kMmaRows - 1) / kMmaRows * nkv * n_requests;
+    const long long thin = (rows + 15) / 16 * nkv * n_requests;
+    const int narrow = shape == 1 ? 0 : shape >= 2 ? 1 : (rows <= 16 || wide < 2 * sms) ? 1 : 0;
+    const int deep = (shape >= 3 || (shape == 0 && narrow && thin <= 2 * sms)) ? 1 : 0;
+    long long ksplit = 1;
+    if (shape == 4) ksplit = 3;
+    else if (shape == 0 && narrow) {
+        ksplit = (2 * sms) / thin;
+        if (ksplit > kMaxParts) ksplit = kMaxParts;
+        if (chunk > 0 && ksplit > (chunk + kMmaKeys - 1) / kMmaKeys) ksplit = (chunk + kMmaKeys - 1) / kMmaKeys;
+        if (ksplit < 1) ksplit = 1;
+    }
+    return narrow | (deep << 1) | ((int)ksplit << 8);
+}
+
+// bfloat16 only; dk and dv multiples of 16, at most 128; sms: the device's multiprocessors (what a small grid is measured against); q, the pages, the gate and out 16-byte aligned
 // with gate_stride even.
 LSB_API int lsb_attention_dv_mma_supported(int dk, int dv) {
     return dk > 0 && dv > 0 && dk % 16 == 0 && dv % 16 == 0 && dk <= 128 && dv <= 128;
@@ -435,37 +544,57 @@ LSB_API int lsb_attention_dv_mma(const void* q, const void* k_pages, const void*
                                  const int* kv_len, const int* table_rows, const int* block_table, int table_stride,
                                  const void* gate, long long gate_stride, void* out, int n_requests, int max_q_len,
                                  int nh, int nkv, int dk, int dv, int page_size, int num_pages, float scale, int window,
-                                 int chunk, cudaStream_t stream) {
+                                 int chunk, int sms, int shape, float* scratch, cudaStream_t stream) {
     if (n_requests <= 0 || max_q_len <= 0) return 0;
+    if (sms <= 0) sms = 148;
     if (!lsb_attention_dv_mma_supported(dk, dv) || nkv <= 0 || nh % nkv || window < 0 || chunk < 0 || n_requests > 65535 ||
         nkv > 65535 || (gate_stride & 1))
         return (int)cudaErrorInvalidValue;
     const int group = nh / nkv;
-    dim3 grid((max_q_len * group + kMmaRows - 1) / kMmaRows, nkv, n_requests);
+    const long long rows = (long long)max_q_len * group;
+    const int plan = lsb_attention_dv_mma_plan(n_requests, max_q_len, nh, nkv, chunk, sms, shape);
+    const int narrow = plan & 1, ksplit = plan >> 8;
+    const bool deep = (plan & 2) != 0;
+    if (ksplit > 1 && !scratch) return (int)cudaErrorInvalidValue;
+    const unsigned tiles = (unsigned)(narrow ? (rows + 15) / 16 : (rows + kMmaRows - 1) / kMmaRows);
+    dim3 grid(tiles * ksplit, nkv, n_requests);
     const float scale_log2 = scale * 1.4426950408889634f;
-#define LSB_DV_MMA(DKP, DVP)                                                                                     \
+#define LSB_DV_MMA(DKP, DVP, STAGES, NARROW)                                                                     \
     do {                                                                                                         \
-        const size_t smem = (size_t)2 * kMmaKeys * ((DKP + 8) + (DVP + 8)) * sizeof(__nv_bfloat16);              \
+        const size_t smem = (size_t)STAGES * kMmaKeys * ((DKP + 8) + (DVP + 8)) * sizeof(__nv_bfloat16);         \
         if (smem > 48 * 1024) {                                                                                  \
-            int rc = (int)cudaFuncSetAttribute(attention_dv_mma_kernel<DKP, DVP>,                                \
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);          \
+            rc = (int)cudaFuncSetAttribute(attention_dv_mma_kernel<DKP, DVP, STAGES, NARROW>,                    \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
             if (rc) return rc;                                                                                   \
         }                                                                                                        \
-        return lsb_launch(attention_dv_mma_kernel<DKP, DVP>, grid, dim3(kMmaThreads), smem, stream, 1,           \
-                          (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, \
-                          q_start, kv_len, table_rows, block_table, table_stride, (const __nv_bfloat16*)gate,    \
-                          gate_stride, (__nv_bfloat16*)out, nh, nkv, dk, dv, page_size, num_pages, scale_log2,   \
-                          window, chunk);                                                                        \
+        rc = lsb_launch(attention_dv_mma_kernel<DKP, DVP, STAGES, NARROW>, grid, dim3(kMmaThreads), smem,        \
+                          stream, 1, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages,                     \
+                          (const __nv_bfloat16*)v_pages, q_start, kv_len, table_rows, block_table, table_stride, \
+                          (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, nh, nkv, dk, dv,         \
+                          page_size, num_pages, scale_log2, window, chunk, ksplit, scratch);                     \
     } while (0)
-    if (dk <= 64) {
-        if (dv <= 64) LSB_DV_MMA(64, 64);
-        else LSB_DV_MMA(64, 128);
-    } else {
-        if (dv <= 64) LSB_DV_MMA(128, 64);
-        else LSB_DV_MMA(128, 128);
-    }
+#define LSB_DV_MMA_SHAPE(DKP, DVP)                                                                               \
+    do {                                                                                                         \
+        if (deep) LSB_DV_MMA(DKP, DVP, 4, true);                                                                 \
+        else if (narrow) LSB_DV_MMA(DKP, DVP, 2, true);                                                          \
+        else LSB_DV_MMA(DKP, DVP, 2, false);                                                                     \
+    } while (0)
+#define LSB_DV_MMA_V(DKP)                                                                                        \
+    do {                                                                                                         \
+        if (dv <= 32) LSB_DV_MMA_SHAPE(DKP, 32);                                                                 \
+        else if (dv <= 64) LSB_DV_MMA_SHAPE(DKP, 64);                                                            \
+        else LSB_DV_MMA_SHAPE(DKP, 128);                                                                         \
+    } while (0)
+    int rc = 0;
+    if (dk <= 64) LSB_DV_MMA_V(64);
+    else LSB_DV_MMA_V(128);
+#undef LSB_DV_MMA_V
+#undef LSB_DV_MMA_SHAPE
 #undef LSB_DV_MMA
-    return 0;
+    if (rc || ksplit <= 1) return rc;
+    return lsb_launch(attention_dv_merge_kernel, dim3(tiles, nkv, n_requests), dim3(kMmaThreads), 0, stream, 1,
+                      (const float*)scratch, q_start, (const __nv_bfloat16*)gate, gate_stride, (__nv_bfloat16*)out, nh, nkv,
+                      dv, ksplit);
 }
 
 LSB_API int lsb_attention_dv_max_dim() { return kDvMaxDim; }

@@ -1149,6 +1149,7 @@ def attention_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, nh: i
           _i(cache.k_pages.shape[0]), _i(1 if store else 0), _stream(proj))
 
 
+DV_BLOCK_SHAPE = 0              # 0: by the grid's size; 1: 64-row blocks; 2, 3: 16-row blocks, two or four tiles in flight; 4: as 3, keys shared by three blocks
 DV_TENSOR_CORES = True          # bfloat16 heads of multiples of 16 up to 128 on warp-level MMA (csrc/attention_dv.cu)
 
 
@@ -1181,10 +1182,23 @@ def attention_dv(q: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, ctx, cach
     if (DV_TENSOR_CORES and q.dtype == torch.bfloat16 and gate_stride % 2 == 0
             and (gate is None or gate.data_ptr() % 4 == 0)
             and _lib("attention_dv").lsb_attention_dv_mma_supported(_i(dk), _i(dv))):
+        # a few blocks only (single tokens, one short portion): the keys of a row tile are shared among
+        # several blocks, whose partial sums meet in a scratch buffer kept for reuse
+        lib = _lib("attention_dv")
+        plan = lib.lsb_attention_dv_mma_plan(_i(ctx.n_requests), _i(ctx.max_q_len), _i(nh), _i(nkv), _i(chunk),
+                                             _i(num_sms(q.device)), _i(DV_BLOCK_SHAPE))
+        scratch = None
+        if plan >> 8 > 1:
+            tiles = -(-ctx.max_q_len * (nh // nkv) // 16)
+            key = ("attention_dv", q.device, ctx.n_requests * nkv * tiles * (plan >> 8) * 16 * (dv + 2))
+            scratch = _scratch.get(key)
+            if scratch is None:
+                scratch = _scratch[key] = torch.empty(key[2], dtype=torch.float32, device=q.device)
         _call("attention_dv", "lsb_attention_dv_mma", _p(q), _p(cache.k_pages), _p(cache.v_pages), _p(ctx.q_start),
               _p(ctx.kv_len), _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(gate),
               _ll(gate_stride), _p(out), _i(ctx.n_requests), _i(ctx.max_q_len), _i(nh), _i(nkv), _i(dk), _i(dv),
-              _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale), _i(window), _i(chunk), _stream(out))
+              _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale), _i(window), _i(chunk), _i(num_sms(q.device)),
+              _i(DV_BLOCK_SHAPE), _p(scratch), _stream(out))
         return
     _call("attention_dv", "lsb_attention_dv_generic", _p(q), _p(cache.k_pages), _p(cache.v_pages), _p(ctx.q_start),
           _p(ctx.kv_len), _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(gate),

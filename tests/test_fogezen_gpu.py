@@ -234,8 +234,14 @@ def test_attention_kernel_one_score_standing_out(dtype, nh, nkv, dk, dv, chunk, 
         gate = torch.randn(sum(q_lens), nh * dv + 6, generator=g).to(dtype).cuda()
         want = torch.cat(outs).reshape(sum(q_lens), nh * dv)
         out = torch.empty(sum(q_lens), nh * dv, dtype=dtype, device="cuda")
-        K.attention_dv(q, nh, nkv, dk, dv, ctx, cache, scale, window, chunk, None, out)
-        assert (out.double().cpu() - want).abs().max() <= tol * 4, targets
+        for shape in ((0, 1, 2, 3, 4) if dtype == torch.bfloat16 else (0,)):       # every block shape of the tile kernel
+            K.DV_BLOCK_SHAPE = shape
+            try:
+                out.zero_()
+                K.attention_dv(q, nh, nkv, dk, dv, ctx, cache, scale, window, chunk, None, out)
+            finally:
+                K.DV_BLOCK_SHAPE = 0
+            assert (out.double().cpu() - want).abs().max() <= tol * 4, (targets, shape)
         K.attention_dv(q, nh, nkv, dk, dv, ctx, cache, scale, window, chunk, gate[:, 6:], out)
         gated = want * torch.sigmoid(gate[:, 6:].double().cpu())
         assert (out.double().cpu() - gated).abs().max() <= tol * 4, targets
