@@ -11,14 +11,14 @@
 //     pages, [page][kv head][offset][dk] and [page][kv head][offset][dv].
 //
 // Each of the first four is optional.  The projections come as rows of one matrix, q at q_off, k
-// at k_off, v at v_off, in the compute dtype.  One block per token, one warp per head at a time;
-// a head waits in shared memory between the norm and the rotation; a token's sines and cosines are
-// formed once and serve all its heads.
+// at k_off, v at v_off, in the compute dtype.  One block per token: all its query and key channels
+// are brought into shared memory in one sweep, then a warp works on a head at a time; a token's
+// sines and cosines are formed once and serve all its heads.
 #include "common.cuh"
 
 LSB_DEFINE_STATUS()
 
-constexpr int kPrepWarps = 4;
+constexpr int kPrepWarps = 8;
 constexpr int kPrepMaxDim = 512;
 
 struct PrepArgs {
@@ -34,7 +34,7 @@ struct PrepArgs {
 
 template <typename T>
 __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArgs a) {
-    __shared__ float head_sh[kPrepWarps][kPrepMaxDim];
+    extern __shared__ float all_sh[];                   // [(nh + nkv) * dk]
     __shared__ float cs_sh[2][kPrepMaxDim / 2];
     lsb_pdl_launch_dependents();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -48,6 +48,17 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArg
         sincosf((float)pos * a.inv_freq[i], &cs_sh[1][i], &cs_sh[0][i]);
     __syncthreads();
     lsb_pdl_wait();                                 // (the block table is written by a kernel of this step)
+    // the first of the token's query and key channels are asked for before the walk through the
+    // block table (three loads that depend on one another), so that the two latencies pass together
+    const T* row = (const T*)a.proj + (size_t)t * a.ld;
+    const int nq = a.nh * a.dk, nall = nq + a.nkv * a.dk;
+    constexpr int kAhead = 4;
+    T ahead[kAhead];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+        const int i = threadIdx.x + u * kPrepWarps * 32;
+        if (i < nall) ahead[u] = row[i < nq ? a.q_off + i : a.k_off + i - nq];
+    }
     long long k_base = -1, v_base = -1;             // element offsets of (page, head 0, offset, 0)
     if (a.store) {
         const int r = a.token_req[t];
@@ -62,26 +73,42 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArg
             v_base = at * a.dv;
         }
     }
-    const T* row = (const T*)a.proj + (size_t)t * a.ld;
     const int half_rot = a.rotary_dim >> 1;
-    float* hs = head_sh[warp];
+    // every query and key channel of the token, with its bias, into shared memory in one sweep (all
+    // loads in flight together); the heads are then worked on from there, a warp per head
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+        const int i = threadIdx.x + u * kPrepWarps * 32;
+        if (i < nall) {
+            const bool is_q = i < nq;
+            const int c = is_q ? i : i - nq;
+            float x = lsb_to_float(ahead[u]);
+            const float* bias = is_q ? a.q_bias : a.k_bias;
+            if (bias) x += bias[c];
+            all_sh[i] = x;
+        }
+    }
+    for (int i = threadIdx.x + kAhead * kPrepWarps * 32; i < nall; i += kPrepWarps * 32) {
+        const bool is_q = i < nq;
+        const int c = is_q ? i : i - nq;
+        float x = lsb_to_float(row[(is_q ? a.q_off : a.k_off) + c]);
+        const float* bias = is_q ? a.q_bias : a.k_bias;
+        if (bias) x += bias[c];
+        all_sh[i] = x;
+    }
+    __syncthreads();
     for (int head = warp; head < a.nh + a.nkv; head += kPrepWarps) {
         const bool is_q = head < a.nh;
         const int hh = is_q ? head : head - a.nh;
-        const T* src = row + (is_q ? a.q_off : a.k_off) + (size_t)hh * a.dk;
-        const float* bias = is_q ? a.q_bias : a.k_bias;
+        const float* hs = all_sh + (size_t)head * a.dk;
         const float* nw = is_q ? a.q_norm : a.k_norm;
-        float ss = 0.f;
-        for (int d = lane; d < a.dk; d += 32) {
-            float x = lsb_to_float(src[d]);
-            if (bias) x += bias[hh * a.dk + d];
-            hs[d] = x;
-            ss += x * x;
-        }
         float inv = 1.f;
-        if (nw) inv = rsqrtf(lsb_warp_sum(ss) / (float)a.dk + a.norm_eps);
+        if (nw) {
+            float ss = 0.f;
+            for (int d = lane; d < a.dk; d += 32) ss += hs[d] * hs[d];
+            inv = rsqrtf(lsb_warp_sum(ss) / (float)a.dk + a.norm_eps);
+        }
         const float mul = is_q ? temp : 1.f;
-        __syncwarp();
         T* dst = nullptr;
         if (is_q) dst = (T*)a.q_out + ((size_t)t * a.nh + hh) * a.dk;
         else if (k_base >= 0) dst = (T*)a.k_pages + k_base + (long long)hh * a.page_size * a.dk;
@@ -105,11 +132,15 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArg
                     x0 = r0;
                     x1 = r1;
                 }
-                dst[ia] = lsb_from_float<T>(x0);
-                if (ib < a.dk) dst[ib] = lsb_from_float<T>(x1);
+                if (ib == ia + 1 && ib < a.dk && (((uintptr_t)(dst + ia)) & (2 * sizeof(T) - 1)) == 0) {
+                    if constexpr (sizeof(T) == 2) *reinterpret_cast<__nv_bfloat162*>(dst + ia) = __floats2bfloat162_rn(x0, x1);
+                    else *reinterpret_cast<float2*>(dst + ia) = make_float2(x0, x1);
+                } else {
+                    dst[ia] = lsb_from_float<T>(x0);
+                    if (ib < a.dk) dst[ib] = lsb_from_float<T>(x1);
+                }
             }
         }
-        __syncwarp();
     }
     if (v_base >= 0) {
         const T* v = row + a.v_off;
@@ -146,7 +177,14 @@ LSB_API int lsb_attention_prep(const void* proj, int dtype, long long ld, int q_
     a.table_stride = table_stride;
     a.q_out = q_out; a.k_pages = k_pages; a.v_pages = v_pages; a.page_size = page_size; a.num_pages = num_pages;
     a.store = store;
-    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(attention_prep_kernel<T>, dim3(tokens), dim3(kPrepWarps * 32), 0, stream,
-                                                1, a));
+    const size_t smem = (size_t)(nh + nkv) * dk * sizeof(float);
+    if (smem > 160 * 1024) return (int)cudaErrorInvalidValue;
+    LSB_DISPATCH_DTYPE(dtype, {
+        if (smem > 32 * 1024) {
+            int rc = (int)cudaFuncSetAttribute(attention_prep_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (rc) return rc;
+        }
+        return lsb_launch(attention_prep_kernel<T>, dim3(tokens), dim3(kPrepWarps * 32), smem, stream, 1, a);
+    });
     return 0;
 }

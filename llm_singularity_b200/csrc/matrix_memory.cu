@@ -68,13 +68,19 @@ memory_gates_kernel(const float* __restrict__ raw, const float* __restrict__ i_b
         for (int c = 0; c < kGatePer; ++c) {
             const int left = t1 - (base + c * 32);              // tokens of this group of 32 (the same on every lane)
             if (left <= 0) break;
-#pragma unroll 8
+            // (all 64 values are fetched before the chain starts: a shuffle issued between two steps of
+            // the chain would make every step wait for it)
+            float fv[32], iv[32];
+#pragma unroll
             for (int l = 0; l < 32; ++l) {
-                const float fj = __shfl_sync(0xffffffffu, gf[c], l);
-                const float ij = __shfl_sync(0xffffffffu, gi[c], l);
+                fv[l] = __shfl_sync(0xffffffffu, gf[c], l);
+                iv[l] = __shfl_sync(0xffffffffu, gi[c], l);
+            }
+#pragma unroll
+            for (int l = 0; l < 32; ++l) {
                 if (l < left) {
                     const float prev = m;
-                    m = fmaxf(fj + m, ij);
+                    m = fmaxf(fv[l] + m, iv[l]);
                     if (l == lane) {
                         before[c] = prev;
                         now[c] = m;
@@ -96,12 +102,125 @@ memory_gates_kernel(const float* __restrict__ raw, const float* __restrict__ i_b
     if (lane == 0) m_state[(size_t)slot * heads + h] = m;
 }
 
-LSB_API int lsb_memory_gates(const float* raw, const float* i_bias, const float* f_bias, float cap, float* m_state,
+// Long portions: the same in three kernels, so that only the chain itself is walked by one warp per
+// (request, head) and everything on either side of it is spread over the chip.
+//   acts:  raw <- (i, f), in place, one thread per value
+//   chain: gates <- (f + m_(t-1) - m_t, i - m_t, m_t), the maxima in order
+//   exps:  gates <- (exp, exp, exp(-.)), in place
+__global__ void __launch_bounds__(256)
+memory_gate_acts_kernel(float* __restrict__ raw, const float* __restrict__ i_bias, const float* __restrict__ f_bias,
+                        float cap, int tokens, int heads) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const long long n = (long long)tokens * 2 * heads;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const int c = (int)(i % (2 * heads));
+        const float z = raw[i];
+        if (c < heads) raw[i] = cap * tanhf((z + (i_bias ? i_bias[c] : 0.f)) / cap);
+        else raw[i] = mm_logsigmoid(cap * tanhf((z + (f_bias ? f_bias[c - heads] : 0.f)) / cap));
+    }
+}
+
+__global__ void __launch_bounds__(32)
+memory_gate_chain_kernel(const float* __restrict__ acts, float* __restrict__ m_state, int n_slots,
+                         const int* __restrict__ q_start, const int* __restrict__ table_rows, float* __restrict__ gates,
+                         int tokens, int heads) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int h = blockIdx.x, r = blockIdx.y, lane = threadIdx.x;
+    const int t0 = q_start[r], t1 = q_start[r + 1];
+    const int slot = table_rows[r];
+    if (slot < 0 || slot >= n_slots) {
+        if (lane == 0) lsb_set_status(LSB_BAD_ROW);
+        return;
+    }
+    float m = m_state[(size_t)slot * heads + h];
+    const size_t plane = (size_t)tokens * heads;
+    float ni[kGatePer], nf[kGatePer];
+    auto fetch = [&](int base) {
+#pragma unroll
+        for (int c = 0; c < kGatePer; ++c) {
+            const int t = base + c * 32 + lane;
+            ni[c] = t < t1 ? acts[(size_t)t * 2 * heads + h] : 0.f;
+            nf[c] = t < t1 ? acts[(size_t)t * 2 * heads + heads + h] : 0.f;
+        }
+    };
+    fetch(t0);
+    for (int base = t0; base < t1; base += 32 * kGatePer) {
+        float gi[kGatePer], gf[kGatePer], before[kGatePer], now[kGatePer];
+#pragma unroll
+        for (int c = 0; c < kGatePer; ++c) {
+            gi[c] = ni[c];
+            gf[c] = nf[c];
+            before[c] = now[c] = 0.f;
+        }
+        if (base + 32 * kGatePer < t1) fetch(base + 32 * kGatePer);
+#pragma unroll
+        for (int c = 0; c < kGatePer; ++c) {
+            const int left = t1 - (base + c * 32);
+            if (left <= 0) break;
+            // (all 64 values are fetched before the chain starts: a shuffle issued between two steps of
+            // the chain would make every step wait for it)
+            float fv[32], iv[32];
+#pragma unroll
+            for (int l = 0; l < 32; ++l) {
+                fv[l] = __shfl_sync(0xffffffffu, gf[c], l);
+                iv[l] = __shfl_sync(0xffffffffu, gi[c], l);
+            }
+#pragma unroll
+            for (int l = 0; l < 32; ++l) {
+                if (l < left) {
+                    const float prev = m;
+                    m = fmaxf(fv[l] + m, iv[l]);
+                    if (l == lane) {
+                        before[c] = prev;
+                        now[c] = m;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < kGatePer; ++c) {
+            const int t = base + c * 32 + lane;
+            if (t < t1) {
+                const size_t at = (size_t)t * heads + h;
+                gates[at] = gf[c] + before[c] - now[c];
+                gates[plane + at] = gi[c] - now[c];
+                gates[2 * plane + at] = now[c];
+            }
+        }
+    }
+    if (lane == 0) m_state[(size_t)slot * heads + h] = m;
+}
+
+__global__ void __launch_bounds__(256)
+memory_gate_exps_kernel(float* __restrict__ gates, long long plane) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < 3 * plane; i += (long long)gridDim.x * blockDim.x)
+        gates[i] = expf(i < 2 * plane ? gates[i] : -gates[i]);
+}
+
+constexpr int kGatesApart = 256;      // portions from this many tokens on take the three kernels
+
+// raw is overwritten where the three kernels run (a step whose longest portion has kGatesApart tokens or more).
+LSB_API int lsb_memory_gates(float* raw, const float* i_bias, const float* f_bias, float cap, float* m_state,
                              int n_slots, const int* q_start, const int* table_rows, int n_requests, float* gates,
-                             int tokens, int heads, cudaStream_t stream) {
+                             int tokens, int heads, int max_q_len, cudaStream_t stream) {
     if (n_requests <= 0 || tokens <= 0) return 0;
     if (heads <= 0 || heads > 65535 || n_requests > 65535 || !(cap > 0.f)) return (int)cudaErrorInvalidValue;
-    return lsb_launch(memory_gates_kernel, dim3(heads, n_requests), dim3(32), 0, stream, 1, raw, i_bias, f_bias, cap,
+    if (max_q_len >= kGatesApart) {
+        const long long n = (long long)tokens * 2 * heads, plane = (long long)tokens * heads;
+        int rc = lsb_launch(memory_gate_acts_kernel, dim3((unsigned)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096)),
+                            dim3(256), 0, stream, 1, raw, i_bias, f_bias, cap, tokens, heads);
+        if (rc) return rc;
+        rc = lsb_launch(memory_gate_chain_kernel, dim3(heads, n_requests), dim3(32), 0, stream, 1, (const float*)raw,
+                        m_state, n_slots, q_start, table_rows, gates, tokens, heads);
+        if (rc) return rc;
+        return lsb_launch(memory_gate_exps_kernel, dim3((unsigned)((3 * plane + 255) / 256 < 4096 ? (3 * plane + 255) / 256 : 4096)),
+                          dim3(256), 0, stream, 1, gates, plane);
+    }
+    return lsb_launch(memory_gates_kernel, dim3(heads, n_requests), dim3(32), 0, stream, 1, (const float*)raw, i_bias, f_bias, cap,
                       m_state, n_slots, q_start, table_rows, gates, tokens, heads);
 }
 

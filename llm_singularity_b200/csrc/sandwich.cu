@@ -18,6 +18,97 @@ LSB_DEFINE_STATUS()
 
 constexpr int kRowThreads = 256;
 
+// four consecutive elements of a row at once (the row's width a multiple of four, 16-byte aligned)
+__device__ __forceinline__ float4 row_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 row_load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void row_store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void row_store4(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<uint32_t*>(&a);
+    raw.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// The same as stream_norm_kernel below with 16-byte accesses.
+template <typename T, bool GATHER>
+__global__ void __launch_bounds__(kRowThreads)
+stream_norm_vec4_kernel(float* __restrict__ residual, const T* __restrict__ y, const float* __restrict__ post_w,
+                        float post_eps, float mult, const float* __restrict__ step, const int* __restrict__ rows,
+                        const float* __restrict__ next_w, float next_eps, T* __restrict__ out, int hidden,
+                        int n_rows_total) {
+    extern __shared__ float row_sh[];
+    __shared__ float scratch[33];
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int r_out = blockIdx.x;
+    int r_in = r_out;
+    if (GATHER) {
+        r_in = rows[r_out];
+        if (r_in < 0 || r_in >= n_rows_total) {
+            if (threadIdx.x == 0) lsb_set_status(LSB_BAD_ROW);
+            if (out)
+                for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)r_out * hidden + i] = lsb_from_float<T>(0.f);
+            return;
+        }
+    }
+    float* res = residual + (size_t)r_in * hidden;
+    const T* yr = y ? y + (size_t)r_in * hidden : nullptr;
+    float inv_y = 1.f;
+    if (yr && post_w) {
+        float ss = 0.f;
+        for (int i = 4 * threadIdx.x; i < hidden; i += 4 * kRowThreads) {
+            const float4 v = row_load4(yr + i);
+            row_store4(row_sh + i, v);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = lsb_block_sum(ss, scratch);
+        inv_y = rsqrtf(ss / (float)hidden + post_eps);
+    }
+    float ss = 0.f;
+    for (int i = 4 * threadIdx.x; i < hidden; i += 4 * kRowThreads) {
+        float4 x = row_load4(res + i);
+        if (yr) {
+            if (post_w) {
+                const float4 v = row_load4(row_sh + i), w = row_load4(post_w + i);
+                x.x += mult * (v.x * inv_y * w.x);
+                x.y += mult * (v.y * inv_y * w.y);
+                x.z += mult * (v.z * inv_y * w.z);
+                x.w += mult * (v.w * inv_y * w.w);
+            } else {
+                const float4 v = row_load4(yr + i);
+                x.x += mult * v.x;
+                x.y += mult * v.y;
+                x.z += mult * v.z;
+                x.w += mult * v.w;
+            }
+        }
+        if (step) {
+            const float4 v = row_load4(step + i);
+            x.x += v.x;
+            x.y += v.y;
+            x.z += v.z;
+            x.w += v.w;
+        }
+        if (!GATHER && (yr || step)) row_store4(res + i, x);
+        row_store4(row_sh + i, x);
+        ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    }
+    if (!out) return;
+    ss = lsb_block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)hidden + next_eps);
+    T* o = out + (size_t)r_out * hidden;
+    for (int i = 4 * threadIdx.x; i < hidden; i += 4 * kRowThreads) {
+        const float4 x = row_load4(row_sh + i), w = row_load4(next_w + i);
+        row_store4(o + i, make_float4(x.x * inv * w.x, x.y * inv * w.y, x.z * inv * w.z, x.w * inv * w.w));
+    }
+}
+
 template <typename T, bool GATHER>
 __global__ void __launch_bounds__(kRowThreads)
 stream_norm_kernel(float* __restrict__ residual, const T* __restrict__ y, const float* __restrict__ post_w,
@@ -77,20 +168,26 @@ LSB_API int lsb_stream_norm(float* residual, const void* y, const float* post_w,
     if (hidden <= 0 || (out && !next_w)) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)hidden * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-#define LSB_STREAM_NORM(G)                                                                            \
+    // 16-byte accesses: rows a multiple of four wide, every operand on a 16-byte boundary
+    bool vec = hidden % 4 == 0;
+    for (const void* ptr : {(const void*)residual, y, (const void*)post_w, (const void*)step, (const void*)next_w, (const void*)out})
+        vec = vec && ((uintptr_t)ptr % 16 == 0);
+#define LSB_STREAM_NORM(KERNEL, G)                                                                    \
     do {                                                                                              \
         if (smem > 48 * 1024) {                                                                       \
-            int rc = (int)cudaFuncSetAttribute(stream_norm_kernel<T, G>,                              \
+            int rc = (int)cudaFuncSetAttribute(KERNEL<T, G>,                                          \
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (rc) return rc;                                                                        \
         }                                                                                             \
-        return lsb_launch(stream_norm_kernel<T, G>, dim3(n_rows), dim3(kRowThreads), smem, stream, 1, residual, \
+        return lsb_launch(KERNEL<T, G>, dim3(n_rows), dim3(kRowThreads), smem, stream, 1, residual,   \
                           (const T*)y, post_w, post_eps, mult, step, rows, next_w, next_eps, (T*)out, hidden,  \
                           n_rows_total);                                                              \
     } while (0)
     LSB_DISPATCH_DTYPE(dtype, {
-        if (rows) LSB_STREAM_NORM(true);
-        else LSB_STREAM_NORM(false);
+        if (vec && rows) LSB_STREAM_NORM(stream_norm_vec4_kernel, true);
+        else if (vec) LSB_STREAM_NORM(stream_norm_vec4_kernel, false);
+        else if (rows) LSB_STREAM_NORM(stream_norm_kernel, true);
+        else LSB_STREAM_NORM(stream_norm_kernel, false);
     });
 #undef LSB_STREAM_NORM
     return 0;

@@ -1212,7 +1212,8 @@ def memory_gates(raw: torch.Tensor, i_bias: Optional[torch.Tensor], f_bias: Opti
     """``raw`` [T, 2 * heads] 32-bit holds the input-gate and then the forget-gate projections.  With
     i = cap * tanh((zi + bi) / cap), f = logsigmoid(cap * tanh((zf + bf) / cap)) and the running
     maximum m_t = max(f + m_(t-1), i) (per request and head, carried in ``m_state`` [slots, heads]),
-    ``gates`` [3, T, heads] receives exp(f + m_(t-1) - m_t), exp(i - m_t) and exp(-m_t)."""
+    ``gates`` [3, T, heads] receives exp(f + m_(t-1) - m_t), exp(i - m_t) and exp(-m_t).  ``raw`` may be
+    overwritten (steps with long portions form the gate activations in place)."""
     _req(raw, "raw", torch.float32, 2)
     _req(m_state, "m_state", torch.float32, 2)
     _req(gates, "gates", torch.float32, 3)
@@ -1226,7 +1227,7 @@ def memory_gates(raw: torch.Tensor, i_bias: Optional[torch.Tensor], f_bias: Opti
                 raise KernelError(f"memory_gates: {name} must have {heads} entries")
     _call("matrix_memory", "lsb_memory_gates", _p(raw), _p(i_bias), _p(f_bias), _f(cap), _p(m_state),
           _i(m_state.shape[0]), _p(ctx.q_start), _p(ctx.table_rows), _i(ctx.n_requests), _p(gates), _i(T), _i(heads),
-          _stream(gates))
+          _i(ctx.max_q_len), _stream(gates))
 
 
 def memory_output(walked: torch.Tensor, floor: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor],
