@@ -20,10 +20,11 @@
 // cp.async, two buffers deep; a warp holds 16 rows' queries as mma.sync A fragments, forms S = Q K^T
 // on the tensor cores (m16n8k16, 32-bit accumulators), does the masked softmax with a running
 // maximum in registers, and feeds the weights straight back as the A fragments of O += P V.
-// Where 64-row blocks would leave most of the chip idle (single tokens: one row per head of the
-// group; one short prompt of a narrow model) a block owns 16 rows instead and its four warps work
-// side by side, each on 16 of a tile's 64 keys, merging through shared memory at the end; the ring
-// of tiles is then four deep where the blocks are few, since such a step waits on memory alone.
+// A step whose requests bring at most 16 rows each (single tokens: one row per head of the group) gets
+// blocks of 16 rows whose four warps work side by side, each on 16 of a tile's 64 keys, merging
+// through shared memory at the end; the ring of tiles is then four deep, and where the blocks are
+// few a row tile's keys are shared among up to eight blocks whose partial sums a second kernel
+// brings together, since such a step waits on memory alone.
 #include "common.cuh"
 
 #include <float.h>
@@ -519,9 +520,11 @@ attention_dv_merge_kernel(const float* __restrict__ scratch, const int* __restri
 LSB_API int lsb_attention_dv_mma_plan(int n_requests, int max_q_len, int nh, int nkv, int chunk, int sms, int shape) {
     if (sms <= 0) sms = 148;
     const long long rows = (long long)max_q_len * (nh / nkv);
-    const long long wide = (rows + kMmaRows - 1) / kMmaRows * nkv * n_requests;
     const long long thin = (rows + 15) / 16 * nkv * n_requests;
-    const int narrow = shape == 1 ? 0 : shape >= 2 ? 1 : (rows <= 16 || wide < 2 * sms) ? 1 : 0;
+    // (16-row blocks for prompt portions were measured too: with the grid small they gain nothing over
+    // 64-row blocks, 56 against 49 us for one prompt of 2,048 tokens and four heads, and lose at any size
+    // that fills the chip, since every block loads whole tiles for a quarter of the arithmetic)
+    const int narrow = shape == 1 ? 0 : shape >= 2 ? 1 : rows <= 16 ? 1 : 0;
     const int deep = (shape >= 3 || (shape == 0 && narrow && thin <= 2 * sms)) ? 1 : 0;
     long long ksplit = 1;
     if (shape == 4) ksplit = 3;
