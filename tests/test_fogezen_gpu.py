@@ -405,3 +405,76 @@ def test_matrix_memory_part_with_carried_state(dtype, heads, D, V, cap):
         else:
             assert (err > 4e-2 * scale).double().mean() <= 0.01 and err.mean() <= 4e-3 * scale, (k, scale, err.mean())
     rt.ops.check_status()
+
+
+# ------------------------------------------------------------------------ as a user runs it
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_memory_walked_in_segments_and_gates_in_three_kernels(tmp_path, dtype):
+    """With segments of 16 tokens every portion of 32 tokens and more is walked segment by segment
+    and chained; the portions of 300 and 255 tokens also take the gates' three-kernel form."""
+    from llm_singularity_b200 import kernels as K
+    old = K.SCAN_SEGMENT
+    K.SCAN_SEGMENT = 16
+    try:
+        cfg = U.CONFIGS["mix_b"]
+        W, path = _setup(tmp_path, cfg, 41)
+        n = 300
+        toks = U.tokens_for(cfg, n, 6)
+        want = U.plain_logits(cfg, W, toks)
+        r = U.make_runner(path, dtype, pages=20)
+        for cuts in ([n], [255, 33, 12], [40, 260]):
+            got = U.run_cuts(r, "g", toks, cuts)
+            assert U.close(got, want, dtype), (cuts, U.rel_err(got, want))
+    finally:
+        K.SCAN_SEGMENT = old
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_replay_as_a_user_runs_it(tmp_path, dtype):
+    """bin/trace_run as a process of its own, fed step by step: seven requests through four slots
+    and a pool smaller than their sum (mixed portions and single tokens), then each request in
+    portions of changing size; every position against the plain model."""
+    import cuttings
+    import numpy as np
+    import replay_util
+    cfg = U.CONFIGS["mix_a"]
+    W, path = _setup(tmp_path, cfg, 23)
+    seqs = {f"q{i}": U.tokens_for(cfg, n, 60 + i) for i, n in enumerate((5, 70, 33, 1, 100, 64, 21))}
+    want = {rid: U.plain_logits(cfg, W, t) for rid, t in seqs.items()}
+    for k, (steps, max_tokens) in enumerate((cuttings.mixed(seqs, seed=3), cuttings.portions(seqs))):
+        out = str(tmp_path / f"out{k}")
+        replay_util.replay_subprocess(path, dtype, steps, out, max_tokens)
+        rows = replay_util.collect(steps, out, cfg["vocab"])
+        assert len(rows) == sum(len(t) for t in seqs.values())
+        for rid, t in seqs.items():
+            got = torch.from_numpy(np.stack([rows[(rid, p)] for p in range(len(t))]))
+            assert U.close(got, want[rid], dtype), (k, rid, U.rel_err(got, want[rid]))
+
+
+def test_command_line_serves_the_design(tmp_path):
+    """bin/llm-serve-llama picks the design by config.json and generates greedily what the plain
+    model picks (where its choice is clear)."""
+    import json
+    import os
+    import subprocess
+    import sys
+    cfg = U.CONFIGS["mix_b"]
+    W, path = _setup(tmp_path, cfg, 29)
+    prompts = [U.tokens_for(cfg, n, 70 + n) for n in (4, 19)]
+    (tmp_path / "p.json").write_text(json.dumps(prompts))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, os.path.join(root, "bin", "llm-serve-llama"), "--model-dir", path, "--dtype", "fp32",
+           "--prompt-ids", str(tmp_path / "p.json"), "--max-new-tokens", "6", "--ignore-eos",
+           "--num-kv-blocks", "16", "--max-batch-size", "2"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr
+    outs = [json.loads(line)["tokens"] for line in res.stdout.splitlines()]
+    assert len(outs) == 2 and all(len(o) == 6 for o in outs)
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for tok in o:
+            logits = U.plain_logits(cfg, W, seq)[-1]
+            top2 = torch.topk(logits, 2).values
+            if top2[0] - top2[1] > 0.05:
+                assert tok == int(logits.argmax())
+            seq.append(tok)
