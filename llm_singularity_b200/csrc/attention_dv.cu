@@ -244,17 +244,19 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     // bytes each).  The row's place in the pages is looked up one tile ahead of the copies that need it,
     // so that the block table's latency passes behind the tile being worked on.
     const int my_row = threadIdx.x >> 1, my_half = threadIdx.x & 1;
-    auto place = [&](int kt) -> long long {
+    // (what `place` returns is not looked at before the copies of the next round use it: a branch on
+    // the page id here would make every round wait for the block table)
+    constexpr int kNoRow = -2, kPastEnd = -1;          // a page id a request never holds / nothing to load
+    auto place = [&](int kt) -> int {
         const int kj = kt * kMmaKeys + my_row;
-        if (kt > kt1 || kj > last_pos) return -1;
+        if (kt > kt1 || kj > last_pos) return kPastEnd;
         const int page = bt[kj / page_size];
-        if (page < 0 || page >= num_pages) {
-            lsb_set_status(LSB_BAD_PAGE);
-            return -1;
-        }
-        return ((long long)page * nkv + g) * page_size + (kj % page_size);
+        return page < 0 ? kNoRow : page;
     };
-    auto load_tile = [&](long long at, int buf) {
+    auto load_tile = [&](int page, int kt, int buf) {
+        long long at = -1;
+        if (page >= num_pages || page == kNoRow) lsb_set_status(LSB_BAD_PAGE);
+        else if (page >= 0) at = ((long long)page * nkv + g) * page_size + ((kt * kMmaKeys + my_row) % page_size);
         __nv_bfloat16* kd = Ks + (buf * kMmaKeys + my_row) * KS;
         __nv_bfloat16* vd = Vs + (buf * kMmaKeys + my_row) * VS;
         const __nv_bfloat16* ksrc = k_pages + (at < 0 ? 0 : at * dk);
@@ -277,16 +279,16 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     // names is the same in every round
 #pragma unroll
     for (int st = 0; st < STAGES - 1; ++st) {
-        if (kt0 + st <= kt1) load_tile(place(kt0 + st), st);
+        if (kt0 + st <= kt1) load_tile(place(kt0 + st), kt0 + st, st);
         else asm volatile("cp.async.commit_group;" ::: "memory");
     }
-    long long at_next = place(kt0 + STAGES - 1);
+    int at_next = place(kt0 + STAGES - 1);
     // rows of this warp see every key of a tile that lies wholly between these two
     const int slab_lo = lowest(p_base + min(slab + 15, rows_total - 1) / group), slab_hi = p_base + slab / group;
     const bool slab_full = slab + 15 < rows_total;
     for (int kt = kt0; kt <= kt1; ++kt) {
         const int buf = (kt - kt0) % STAGES;
-        if (kt + STAGES - 1 <= kt1) load_tile(at_next, (kt - kt0 + STAGES - 1) % STAGES);
+        if (kt + STAGES - 1 <= kt1) load_tile(at_next, kt + STAGES - 1, (kt - kt0 + STAGES - 1) % STAGES);
         else asm volatile("cp.async.commit_group;" ::: "memory");
         at_next = place(kt + STAGES);
         asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");

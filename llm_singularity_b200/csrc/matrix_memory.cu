@@ -238,17 +238,35 @@ memory_output_kernel(const float* __restrict__ walked, const float* __restrict__
     if (item >= (long long)tokens * heads) return;
     const int t = (int)(item / heads), h = (int)(item % heads);
     const float* w = walked + (size_t)item * (V + 1);
-    const float denom = fmaxf(fabsf(w[V]), floor_[item]) + 1e-6f;
+    // one reciprocal for the row, and the row read once: a lane keeps up to kOutRegs of its values
+    const float rden = 1.f / (fmaxf(fabsf(w[V]), floor_[item]) + 1e-6f);
+    constexpr int kOutRegs = 8;
+    float keep[kOutRegs];
     float ss = 0.f;
-    for (int c = lane; c < V; c += 32) {
-        const float o = w[c] / denom;
+#pragma unroll
+    for (int u = 0; u < kOutRegs; ++u) {
+        const int c = lane + 32 * u;
+        keep[u] = c < V ? w[c] * rden : 0.f;
+        ss += keep[u] * keep[u];
+    }
+    for (int c = lane + 32 * kOutRegs; c < V; c += 32) {
+        const float o = w[c] * rden;
         ss += o * o;
     }
     const float inv = rsqrtf(lsb_warp_sum(ss) / (float)V + eps);
     const T* g = gate ? gate + (size_t)t * gate_stride + (size_t)h * V : nullptr;
     T* y = out + ((size_t)t * heads + h) * V;
-    for (int c = lane; c < V; c += 32) {
-        float v = w[c] / denom * inv * weight[h * V + c];
+#pragma unroll
+    for (int u = 0; u < kOutRegs; ++u) {
+        const int c = lane + 32 * u;
+        if (c < V) {
+            float v = keep[u] * inv * weight[h * V + c];
+            if (g) v *= 1.f / (1.f + expf(-lsb_to_float(g[c])));
+            y[c] = lsb_from_float<T>(v);
+        }
+    }
+    for (int c = lane + 32 * kOutRegs; c < V; c += 32) {
+        float v = w[c] * rden * inv * weight[h * V + c];
         if (g) v *= 1.f / (1.f + expf(-lsb_to_float(g[c])));
         y[c] = lsb_from_float<T>(v);
     }

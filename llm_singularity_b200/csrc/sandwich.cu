@@ -232,6 +232,61 @@ branch_mean_kernel(Branches br, float eps, T* __restrict__ out, int hidden) {
     }
 }
 
+// The same with 16-byte accesses and every branch's row read once: a thread keeps its share of each
+// branch (rows up to kBranchRegs * 4 * 256 wide) between the sums of squares and the mean.
+constexpr int kBranchRegs = 2;
+
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+branch_mean_vec4_kernel(Branches br, float eps, T* __restrict__ out, int hidden) {
+    __shared__ float scratch[33];
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const size_t base = (size_t)blockIdx.x * hidden;
+    float4 keep[kMaxBranches][kBranchRegs];
+    float inv[kMaxBranches];
+#pragma unroll
+    for (int b = 0; b < kMaxBranches; ++b) {
+#pragma unroll
+        for (int u = 0; u < kBranchRegs; ++u) {
+            const int i = 4 * (threadIdx.x + u * kRowThreads);
+            keep[b][u] = (b < br.n && i < hidden) ? row_load4((const T*)br.y[b] + base + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < kMaxBranches; ++b) {
+        inv[b] = 0.f;
+        if (b < br.n) {
+            float ss = 0.f;
+#pragma unroll
+            for (int u = 0; u < kBranchRegs; ++u)
+                ss += keep[b][u].x * keep[b][u].x + keep[b][u].y * keep[b][u].y + keep[b][u].z * keep[b][u].z +
+                      keep[b][u].w * keep[b][u].w;
+            ss = lsb_block_sum(ss, scratch);
+            inv[b] = rsqrtf(ss / (float)hidden + eps);
+        }
+    }
+    const float share = 1.f / (float)br.n;
+#pragma unroll
+    for (int u = 0; u < kBranchRegs; ++u) {
+        const int i = 4 * (threadIdx.x + u * kRowThreads);
+        if (i < hidden) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int b = 0; b < kMaxBranches; ++b) {
+                if (b < br.n) {
+                    const float4 w = row_load4(br.w[b] + i);
+                    acc.x += keep[b][u].x * inv[b] * w.x;
+                    acc.y += keep[b][u].y * inv[b] * w.y;
+                    acc.z += keep[b][u].z * inv[b] * w.z;
+                    acc.w += keep[b][u].w * inv[b] * w.w;
+                }
+            }
+            row_store4(out + base + i, make_float4(acc.x * share, acc.y * share, acc.z * share, acc.w * share));
+        }
+    }
+}
+
 LSB_API int lsb_branch_max() { return kMaxBranches; }
 
 // ys, ws: n pointers each (rows of the branches in the compute dtype, their 32-bit weights).
@@ -245,7 +300,11 @@ LSB_API int lsb_branch_mean(const void* const* ys, const float* const* ws, int n
         br.y[b] = b < n ? ys[b] : nullptr;
         br.w[b] = b < n ? ws[b] : nullptr;
     }
-    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(branch_mean_kernel<T>, dim3(n_rows), dim3(kRowThreads), 0, stream, 1,
-                                                br, eps, (T*)out, hidden));
+    bool vec = hidden % 4 == 0 && hidden <= kBranchRegs * 4 * kRowThreads && (uintptr_t)out % 16 == 0;
+    for (int b = 0; b < n; ++b) vec = vec && (uintptr_t)ys[b] % 16 == 0 && (uintptr_t)ws[b] % 16 == 0;
+    LSB_DISPATCH_DTYPE(dtype, {
+        if (vec) return lsb_launch(branch_mean_vec4_kernel<T>, dim3(n_rows), dim3(kRowThreads), 0, stream, 1, br, eps, (T*)out, hidden);
+        return lsb_launch(branch_mean_kernel<T>, dim3(n_rows), dim3(kRowThreads), 0, stream, 1, br, eps, (T*)out, hidden);
+    });
     return 0;
 }
