@@ -30,6 +30,28 @@ struct PrepArgs {
     const float* inv_freq; int rotary_dim, adjacent;
     const int *positions, *token_req, *table_rows, *block_table; int table_stride;
     void *q_out, *k_pages, *v_pages; int page_size, num_pages, store;
+    int vec;        // 16-byte loads of the projections: every offset, ld, dk and dv a multiple of 16 bytes
+};
+
+// 16 bytes of T as floats
+template <typename T> struct PrepVec;
+template <> struct PrepVec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void widen(const uint4& raw, float (&f)[4]) {
+        f[0] = __uint_as_float(raw.x); f[1] = __uint_as_float(raw.y); f[2] = __uint_as_float(raw.z); f[3] = __uint_as_float(raw.w);
+    }
+};
+template <> struct PrepVec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void widen(const uint4& raw, float (&f)[8]) {
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 v = __bfloat1622float2(p[j]);
+            f[2 * j] = v.x;
+            f[2 * j + 1] = v.y;
+        }
+    }
 };
 
 template <typename T>
@@ -47,24 +69,33 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArg
     for (int i = threadIdx.x; i < (a.rotary_dim >> 1); i += blockDim.x)
         sincosf((float)pos * a.inv_freq[i], &cs_sh[1][i], &cs_sh[0][i]);
     __syncthreads();
+    const int slot_row = a.store ? a.table_rows[a.token_req[t]] : 0;      // (metadata too)
     lsb_pdl_wait();                                 // (the block table is written by a kernel of this step)
-    // the first of the token's query and key channels are asked for before the walk through the
-    // block table (three loads that depend on one another), so that the two latencies pass together
+    // the first of the token's query and key channels are asked for before the block table is, so that
+    // the two latencies pass together
     const T* row = (const T*)a.proj + (size_t)t * a.ld;
     const int nq = a.nh * a.dk, nall = nq + a.nkv * a.dk;
-    constexpr int kAhead = 4;
+    constexpr int kAhead = 4, VEC = PrepVec<T>::N;
     T ahead[kAhead];
+    uint4 ahead_v[2];
+    if (a.vec) {
 #pragma unroll
-    for (int u = 0; u < kAhead; ++u) {
-        const int i = threadIdx.x + u * kPrepWarps * 32;
-        if (i < nall) ahead[u] = row[i < nq ? a.q_off + i : a.k_off + i - nq];
+        for (int u = 0; u < 2; ++u) {
+            const int i = (threadIdx.x + u * kPrepWarps * 32) * VEC;
+            if (i < nall) ahead_v[u] = *reinterpret_cast<const uint4*>(row + (i < nq ? a.q_off + i : a.k_off + i - nq));
+        }
+    } else {
+#pragma unroll
+        for (int u = 0; u < kAhead; ++u) {
+            const int i = threadIdx.x + u * kPrepWarps * 32;
+            if (i < nall) ahead[u] = row[i < nq ? a.q_off + i : a.k_off + i - nq];
+        }
     }
     long long k_base = -1, v_base = -1;             // element offsets of (page, head 0, offset, 0)
     if (a.store) {
-        const int r = a.token_req[t];
         const int page_idx = pos / a.page_size;
         int page = -1;
-        if (page_idx < a.table_stride) page = a.block_table[(size_t)a.table_rows[r] * a.table_stride + page_idx];
+        if (page_idx < a.table_stride) page = a.block_table[(size_t)slot_row * a.table_stride + page_idx];
         if (page < 0 || page >= a.num_pages) {
             if (threadIdx.x == 0) lsb_set_status(LSB_BAD_PAGE);
         } else {
@@ -76,10 +107,28 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArg
     const int half_rot = a.rotary_dim >> 1;
     // every query and key channel of the token, with its bias, into shared memory in one sweep (all
     // loads in flight together); the heads are then worked on from there, a warp per head
+    auto stage_vec = [&](int i, const uint4& raw) {
+        const bool is_q = i < nq;
+        const int c = is_q ? i : i - nq;
+        float f[VEC];
+        PrepVec<T>::widen(raw, f);
+        const float* bias = is_q ? a.q_bias : a.k_bias;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) all_sh[i + e] = bias ? f[e] + bias[c + e] : f[e];
+    };
+    if (a.vec) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int i = (threadIdx.x + u * kPrepWarps * 32) * VEC;
+            if (i < nall) stage_vec(i, ahead_v[u]);
+        }
+        for (int i = (threadIdx.x + 2 * kPrepWarps * 32) * VEC; i < nall; i += kPrepWarps * 32 * VEC)
+            stage_vec(i, *reinterpret_cast<const uint4*>(row + (i < nq ? a.q_off + i : a.k_off + i - nq)));
+    }
 #pragma unroll
     for (int u = 0; u < kAhead; ++u) {
         const int i = threadIdx.x + u * kPrepWarps * 32;
-        if (i < nall) {
+        if (!a.vec && i < nall) {
             const bool is_q = i < nq;
             const int c = is_q ? i : i - nq;
             float x = lsb_to_float(ahead[u]);
@@ -88,7 +137,7 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArg
             all_sh[i] = x;
         }
     }
-    for (int i = threadIdx.x + kAhead * kPrepWarps * 32; i < nall; i += kPrepWarps * 32) {
+    for (int i = a.vec ? nall : threadIdx.x + kAhead * kPrepWarps * 32; i < nall; i += kPrepWarps * 32) {
         const bool is_q = i < nq;
         const int c = is_q ? i : i - nq;
         float x = lsb_to_float(row[(is_q ? a.q_off : a.k_off) + c]);
@@ -142,7 +191,14 @@ __global__ void __launch_bounds__(kPrepWarps * 32) attention_prep_kernel(PrepArg
             }
         }
     }
-    if (v_base >= 0) {
+    if (v_base >= 0 && a.vec && !a.v_bias) {
+        const T* v = row + a.v_off;
+        for (int w = threadIdx.x * VEC; w < a.nkv * a.dv; w += blockDim.x * VEC) {
+            const int head = w / a.dv, d = w - head * a.dv;
+            *reinterpret_cast<uint4*>((T*)a.v_pages + v_base + (long long)head * a.page_size * a.dv + d) =
+                *reinterpret_cast<const uint4*>(v + w);
+        }
+    } else if (v_base >= 0) {
         const T* v = row + a.v_off;
         for (int w = threadIdx.x; w < a.nkv * a.dv; w += blockDim.x) {
             const int head = w / a.dv, d = w - head * a.dv;
@@ -177,6 +233,9 @@ LSB_API int lsb_attention_prep(const void* proj, int dtype, long long ld, int q_
     a.table_stride = table_stride;
     a.q_out = q_out; a.k_pages = k_pages; a.v_pages = v_pages; a.page_size = page_size; a.num_pages = num_pages;
     a.store = store;
+    const int per16 = dtype == LSB_F32 ? 4 : 8;
+    a.vec = ((uintptr_t)proj % 16 == 0 && (uintptr_t)v_pages % 16 == 0 && ld % per16 == 0 && q_off % per16 == 0 &&
+             k_off % per16 == 0 && v_off % per16 == 0 && dk % per16 == 0 && dv % per16 == 0) ? 1 : 0;
     const size_t smem = (size_t)(nh + nkv) * dk * sizeof(float);
     if (smem > 160 * 1024) return (int)cudaErrorInvalidValue;
     LSB_DISPATCH_DTYPE(dtype, {
