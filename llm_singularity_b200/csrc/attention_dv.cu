@@ -244,8 +244,8 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     // bytes each).  The row's place in the pages is looked up one tile ahead of the copies that need it,
     // so that the block table's latency passes behind the tile being worked on.
     const int my_row = threadIdx.x >> 1, my_half = threadIdx.x & 1;
-    // (what `place` returns is not looked at before the copies of the next round use it: a branch on
-    // the page id here would make every round wait for the block table)
+    // (what `place` returns is not looked at before the copies of the next turn of the loop use it: a
+    // branch on the page id here would make every turn wait for the block table)
     constexpr int kNoRow = -2, kPastEnd = -1;          // a page id a request never holds / nothing to load
     auto place = [&](int kt) -> int {
         const int kj = kt * kMmaKeys + my_row;
@@ -276,7 +276,7 @@ attention_dv_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         for (int c = dv; c < DVP; ++c) Vs[idx * VS + c] = __float2bfloat16_rn(0.f);
     }
     // a group of copies is committed for every tile slot, real or not, so that the count the wait
-    // names is the same in every round
+    // names is the same in every turn of the loop
 #pragma unroll
     for (int st = 0; st < STAGES - 1; ++st) {
         if (kt0 + st <= kt1) load_tile(place(kt0 + st), kt0 + st, st);

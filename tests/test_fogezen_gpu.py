@@ -190,7 +190,7 @@ def _fill(cache, row, K, V):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("nh, nkv, dk, dv, chunk, window, page", [(4, 2, 32, 16, 24, 0, 16), (6, 1, 96, 32, 40, 0, 16),
+@pytest.mark.parametrize("nh, nkv, dk, dv, chunk, window, page", [(4, 2, 32, 16, 24, 0, 16), (6, 2, 96, 48, 40, 0, 16),
                                                                   (3, 3, 10, 14, 5, 0, 8), (4, 1, 64, 128, 0, 0, 16),
                                                                   (2, 2, 128, 64, 33, 21, 16), (8, 2, 48, 80, 64, 0, 32),
                                                                   (20, 1, 80, 48, 50, 0, 16), (5, 5, 112, 16, 7, 0, 8)])
